@@ -1,0 +1,4 @@
+"""hk_b200: a small, whole inference engine for the Qwen3 dense decoder on one B200."""
+from . import models  # noqa: F401  (registers the architectures)
+
+__version__ = "0.1.0"

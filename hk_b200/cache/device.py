@@ -1,0 +1,101 @@
+"""The cache on the GPU: page tensors, block tables and state arrays, driven by `CacheBooks`.
+
+Layout of a group's pages, per schedule entry of the group: keys and values each
+[num_pages, n_kv_heads, page_tokens, head_dim] in the compute type, so one (page, kv head)
+slab of page_tokens * head_dim elements is contiguous.  (The reference keeps a fixed region
+per slot, [layer][kv head][position][head_dim]: src/cuda/engine.zig:234,393-401.)  The block
+table of a group is int32 [max_requests, max_pages_per_request] on the device, a copy of the
+host books' table; rows that changed are uploaded before a step runs.  A mixer with state of
+fixed size gets an array [max_requests, *shape], zeroed when a request takes its slot.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..parts.base import KVCacheSpec, Precision, StateSpec
+from .pages import CacheBooks
+
+
+@dataclass
+class LayerCache:
+    """What one schedule entry's mixer is handed."""
+    kind: str                                  # "pages", "state" or "none"
+    k_pages: Optional[torch.Tensor] = None
+    v_pages: Optional[torch.Tensor] = None
+    block_table: Optional[torch.Tensor] = None
+    page_tokens: int = 0
+    window: Optional[int] = None
+    state: Optional[torch.Tensor] = None
+    group: int = -1
+
+
+class PagedCache:
+    def __init__(self, cache_specs: Sequence[object], precision: Precision, page_tokens: int, num_pages: int,
+                 max_requests: int, max_context: int):
+        self.precision = precision
+        self.page_tokens = page_tokens
+        self.num_pages = num_pages
+        keys: List[tuple] = []
+        entry_group: List[int] = []
+        for spec in cache_specs:
+            if isinstance(spec, KVCacheSpec):
+                key = (spec.n_kv_heads, spec.head_dim, spec.window)
+                if key not in keys:
+                    keys.append(key)
+                entry_group.append(keys.index(key))
+            else:
+                entry_group.append(-1)
+        self.books = CacheBooks([k[2] for k in keys], page_tokens, num_pages, max_requests, max_context)
+        dev = precision.device
+        self.tables = [torch.full((max_requests, self.books.max_pages_per_request), -1, dtype=torch.int32, device=dev)
+                       for _ in keys]
+        self.layers: List[LayerCache] = []
+        self._states: List[torch.Tensor] = []
+        for spec, gi in zip(cache_specs, entry_group):
+            if isinstance(spec, KVCacheSpec):
+                shape = (num_pages, spec.n_kv_heads, page_tokens, spec.head_dim)
+                # zeros, not empty: a page that was never written must not hold NaN patterns
+                self.layers.append(LayerCache(
+                    "pages", torch.zeros(shape, dtype=precision.compute, device=dev),
+                    torch.zeros(shape, dtype=precision.compute, device=dev), self.tables[gi], page_tokens,
+                    spec.window, None, gi))
+            elif isinstance(spec, StateSpec):
+                st = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=dev)
+                self._states.append(st)
+                self.layers.append(LayerCache("state", state=st))
+            elif spec is None:
+                self.layers.append(LayerCache("none"))
+            else:
+                raise TypeError(f"a mixer's cache_spec() gave {type(spec).__name__}; KVCacheSpec, StateSpec or None are known")
+
+    # -- requests ----------------------------------------------------------------------------
+    def open(self) -> int:
+        slot = self.books.open()
+        for st in self._states:
+            st[slot].zero_()
+        return slot
+
+    def close(self, slot: int) -> None:
+        self.books.close(slot)
+
+    def sync_tables(self) -> None:
+        """Uploads the block-table rows that changed since the last call.  The copies read
+        pageable host memory, so they are complete (staged) when the call returns and the
+        books may change again at once."""
+        if not self.books.dirty:
+            return
+        for slot in sorted(self.books.dirty):
+            for g, dev_table in zip(self.books.groups, self.tables):
+                dev_table[slot].copy_(torch.from_numpy(g.table[slot].copy()))
+        self.books.dirty.clear()
+
+    def bytes(self) -> int:
+        n = 0
+        for lc in self.layers:
+            for t in (lc.k_pages, lc.v_pages, lc.state):
+                if t is not None:
+                    n += t.numel() * t.element_size()
+        return n

@@ -1,0 +1,170 @@
+"""Builds the CUDA sources of this folder for sm_100a with nvcc and loads them with ctypes.
+
+Every library is one `.cu` file compiled alone (no framework headers, so a file takes
+seconds).  Built files live in `_build/` beside the sources, named by a hash of the
+source text and flags, so a changed source is rebuilt and a built file is found again
+by the next process.  A library is compiled when it is first asked for: a model that
+runs in 32-bit never compiles the bfloat16 tensor-core kernels.  While nvcc runs, a
+line goes to stderr now and then.  There is no fallback: without nvcc, or when a
+source does not compile, `load` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from typing import Dict, List
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+# library name -> source file; headers every library depends on
+LIBRARIES: Dict[str, str] = {
+    "elementwise": "elementwise.cu",
+    "gemm_generic": "gemm_generic.cu",
+    "attention_generic": "attention_generic.cu",
+    "sampling": "sampling.cu",
+    "gemm_tc": "gemm_tc.cu",
+    "gemm_smallm": "gemm_smallm.cu",
+    "attention_flash": "attention_flash.cu",
+}
+HEADERS: List[str] = ["common.cuh"]
+
+_loaded: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def find_nvcc() -> str:
+    cands = []
+    if os.environ.get("HK_B200_NVCC"):
+        cands.append(os.environ["HK_B200_NVCC"])
+    for var in ("CUDA_HOME", "CUDA_PATH"):
+        if os.environ.get(var):
+            cands.append(os.path.join(os.environ[var], "bin", "nvcc"))
+    cands.append("/usr/local/cuda/bin/nvcc")
+    w = shutil.which("nvcc")
+    if w:
+        cands.append(w)
+    for c in cands:
+        if os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    raise BuildError("nvcc was not found (looked at HK_B200_NVCC, CUDA_HOME, /usr/local/cuda, PATH); "
+                     "the CUDA kernels cannot be built and there is no fallback")
+
+
+def build_dir() -> str:
+    d = os.environ.get("HK_B200_BUILD_DIR") or os.path.join(HERE, "_build")
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.unlink(probe)
+        return d
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"hk_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _digest(name: str) -> str:
+    h = hashlib.sha256()
+    for fn in [LIBRARIES[name]] + HEADERS:
+        with open(os.path.join(HERE, fn), "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def library_path(name: str) -> str:
+    return os.path.join(build_dir(), f"libhk_{name}.{_digest(name)}.so")
+
+
+def _say(msg: str) -> None:
+    print(f"[hk_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def build(name: str, verbose: bool = True) -> str:
+    """Compiles library `name` if its built file is absent; returns the file's path."""
+    if name not in LIBRARIES:
+        raise BuildError(f"no CUDA library named '{name}'")
+    out = library_path(name)
+    if os.path.isfile(out):
+        return out
+    nvcc = find_nvcc()
+    src = os.path.join(HERE, LIBRARIES[name])
+    tmp = f"{out}.{os.getpid()}.tmp"
+    cmd = [nvcc] + NVCC_FLAGS + ["-I", HERE, "-o", tmp, src]
+    if verbose:
+        _say(f"compiling {LIBRARIES[name]} for sm_100a ...")
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    done = threading.Event()
+
+    def ticker():
+        while not done.wait(10.0):
+            if verbose:
+                _say(f"still compiling {LIBRARIES[name]} ({time.time() - t0:.0f} s)")
+
+    th = threading.Thread(target=ticker, daemon=True)
+    th.start()
+    try:
+        log, _ = proc.communicate()
+    finally:
+        done.set()
+    if proc.returncode != 0:
+        try:
+            os.unlink(tmp)
+        except OSError:
+            pass
+        raise BuildError(f"nvcc failed on {LIBRARIES[name]} (exit {proc.returncode}):\n{log}")
+    os.replace(tmp, out)
+    if verbose:
+        _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
+    return out
+
+
+def build_many(names, verbose: bool = True) -> None:
+    """Compiles several libraries side by side (one nvcc process each)."""
+    errors = []
+    threads = []
+
+    def run(n):
+        try:
+            build(n, verbose)
+        except Exception as e:  # noqa: BLE001 - reported below
+            errors.append(e)
+
+    for n in names:
+        if not os.path.isfile(library_path(n)):
+            t = threading.Thread(target=run, args=(n,))
+            t.start()
+            threads.append(t)
+    for t in threads:
+        t.join()
+    if errors:
+        raise errors[0]
+
+
+def load(name: str) -> ctypes.CDLL:
+    """The loaded library `name`, compiled first if need be."""
+    with _lock:
+        lib = _loaded.get(name)
+        if lib is None:
+            lib = ctypes.CDLL(build(name))
+            _loaded[name] = lib
+        return lib

@@ -1,0 +1,205 @@
+// Row-wise kernels of the decoder: embedding gather, RMS norm, the fused per-head
+// norm + rotation + paged cache write, and SwiGLU.  Each is templated on the storage
+// type (float for the true 32-bit path, bf16 for serving); all arithmetic is fp32.
+//
+// Reference counterparts (one launch each there, none fused): `rms_norm`
+// src/cuda_device.zig:1393-1403, `head_norm` :1406-1415, `rope` :1420-1441,
+// `kv_write` :1453-1477, `swiglu` :1824-1829; host-side embedding
+// src/cuda/engine.zig:724-737.  The fusion of norm + rotation + cache write follows
+// the idea of shaders/rope_kv.comp:2-7.
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] widened to fp32 (the residual stream is fp32).
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int n, int d, int vocab) {
+  int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;  // the host validates ids; this only keeps the read in bounds
+  const T* src = table + (size_t)id * d;
+  float* dst = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+HK_API int hk_embedding(const void* table, int table_dtype, const int* ids, float* out, int n, int d,
+                        int vocab, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == HK_F32)
+    embedding_kernel<float><<<n, threads, 0, s>>>((const float*)table, ids, out, n, d, vocab);
+  else if (table_dtype == HK_BF16)
+    embedding_kernel<bf16><<<n, threads, 0, s>>>((const bf16*)table, ids, out, n, d, vocab);
+  else
+    return HK_ERR_UNSUPPORTED;
+  return hk_launch_status();
+}
+
+// ----------------------------------------------------------------------------- rms norm
+// out[r, :] = x[row(r), :] * rsqrt(mean(x^2) + eps) * w, with row(r) = rows ? rows[r] : r.
+// The sum of squares runs in a fixed order (thread-strided partials, warp tree, then
+// warps in order), so a row's result does not depend on what else is in the batch.
+template <typename TO>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                const int* __restrict__ rows, TO* __restrict__ out, int d, float eps) {
+  __shared__ float warp_part[32];
+  __shared__ float inv_s;
+  int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = src[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) warp_part[wid] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += warp_part[i];
+    inv_s = 1.0f / sqrtf(tot / (float)d + eps);
+  }
+  __syncthreads();
+  float inv = inv_s;
+  TO* dst = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<TO>(src[i] * inv * w[i]);
+}
+
+HK_API int hk_rms_norm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
+                       int n_out, int d, float eps, void* stream) {
+  if (n_out <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  int threads = d >= 2048 ? 256 : 128;
+  if (out_dtype == HK_F32)
+    rms_norm_kernel<float><<<n_out, threads, 0, s>>>(x, w, rows, (float*)out, d, eps);
+  else if (out_dtype == HK_BF16)
+    rms_norm_kernel<bf16><<<n_out, threads, 0, s>>>(x, w, rows, (bf16*)out, d, eps);
+  else
+    return HK_ERR_UNSUPPORTED;
+  return hk_launch_status();
+}
+
+// ------------------------------------------------- per-head norm + rotation + cache write
+// One warp per (token, head) of the fused projection output qkv[n, (H + 2G) * hd] (fp32):
+//   q heads: optional RMS norm over hd (weight shared by the heads), rotate-half rotation of
+//            the first `rot` dims by the token's position, stored to q_out[n, H*hd];
+//   k heads: the same with the key norm weight, stored into the token's cache page;
+//   v heads: stored into the cache page unchanged.
+// Page of a token: block_table[slot_of_token[t]][pos / page_tokens]; the cache layout is
+// [page][G][page_tokens][hd].  With write_kv == 0 only q is produced (a layer that reads
+// another layer's cache).
+#define QKR_MAX_HD 256
+#define QKR_WARPS 4
+
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(
+    const float* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_w,
+    const float* __restrict__ k_w, float eps, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
+    const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
+    T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
+    int write_kv) {
+  __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int heads_total = H + (write_kv ? 2 * G : 0);
+  long long item = (long long)blockIdx.x * QKR_WARPS + wid;
+  if (item >= (long long)n * heads_total) return;
+  int t = (int)(item / heads_total);
+  int hh = (int)(item % heads_total);
+  const float* src = qkv + (size_t)t * (H + 2 * G) * hd + (size_t)hh * hd;
+  float* v = buf[wid];
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) {
+    float a = src[i];
+    v[i] = a;
+    ss = fmaf(a, a, ss);
+  }
+  __syncwarp();
+  int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);  // q, k, v
+  int pos = positions[t];
+  if (kind != 2) {
+    const float* w = kind == 0 ? q_w : k_w;
+    if (w) {
+      ss = warp_sum(ss);
+      float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+      for (int i = lane; i < hd; i += 32) v[i] = v[i] * inv * w[i];
+      __syncwarp();
+    }
+    if (rot > 0) {
+      int half = rot >> 1;
+      const float* c = cos_t + (size_t)pos * half;
+      const float* s = sin_t + (size_t)pos * half;
+      for (int i = lane; i < half; i += 32) {
+        float a = v[i], b = v[i + half];
+        float ci = c[i], si = s[i];
+        v[i] = a * ci - b * si;
+        v[i + half] = a * si + b * ci;
+      }
+      __syncwarp();
+    }
+  }
+  T* dst;
+  if (kind == 0) {
+    dst = q_out + (size_t)t * H * hd + (size_t)hh * hd;
+  } else {
+    int g = kind == 1 ? hh - H : hh - H - G;
+    int page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
+    if (page < 0) return;  // the host never schedules this; keeps a stale table from writing out of bounds
+    T* base = kind == 1 ? k_pages : v_pages;
+    dst = base + (((size_t)page * G + g) * page_tokens + (pos % page_tokens)) * hd;
+  }
+  for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(v[i]);
+}
+
+HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, const float* q_w,
+                                    const float* k_w, float eps, const float* cos_t, const float* sin_t,
+                                    int rot, const int* positions, const int* slot_of_token,
+                                    const int* block_table, int table_stride, void* k_pages,
+                                    void* v_pages, int n, int H, int G, int hd, int page_tokens,
+                                    int write_kv, void* stream) {
+  if (n <= 0) return 0;
+  if (hd > QKR_MAX_HD || hd < 2 || rot > hd || (rot & 1)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  long long items = (long long)n * (H + (write_kv ? 2 * G : 0));
+  unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
+  if (dtype == HK_F32)
+    qk_norm_rope_kv_write_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
+        qkv, (float*)q_out, q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table,
+        table_stride, (float*)k_pages, (float*)v_pages, n, H, G, hd, page_tokens, write_kv);
+  else if (dtype == HK_BF16)
+    qk_norm_rope_kv_write_kernel<bf16><<<blocks, QKR_WARPS * 32, 0, s>>>(
+        qkv, (bf16*)q_out, q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table,
+        table_stride, (bf16*)k_pages, (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv);
+  else
+    return HK_ERR_UNSUPPORTED;
+  return hk_launch_status();
+}
+
+// ----------------------------------------------------------------------------- swiglu
+// out[t, j] = silu(gu[t, j]) * gu[t, F + j] for the fused projection gu[n, 2F] (gate | up).
+template <typename TO>
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  long long t = i / F;
+  int j = (int)(i % F);
+  float g = gu[t * 2 * F + j];
+  float u = gu[t * 2 * F + F + j];
+  out[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+}
+
+HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  long long total = (long long)n * F;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (out_dtype == HK_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, (float*)out, total, F);
+  else if (out_dtype == HK_BF16)
+    swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, (bf16*)out, total, F);
+  else
+    return HK_ERR_UNSUPPORTED;
+  return hk_launch_status();
+}

@@ -1,0 +1,246 @@
+"""Python face of the CUDA kernels: argument checks, kernel choice, launch on torch's
+current stream.
+
+Every function takes torch CUDA tensors, checks what the kernel assumes (device, dtype,
+contiguity, sizes) and raises `KernelError` with a clear message when a kernel refuses a
+shape; nothing falls back to the CPU or to a library.  Kernel choice (tensor-core GEMM or
+generic GEMM, flash or generic attention) is by shape alone, never by batch content, and
+can be pinned with `force()` by tests.
+"""
+from __future__ import annotations
+
+import contextlib
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_ERR_UNSUPPORTED = 100001
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, not {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, not {t.dim()}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == _ERR_UNSUPPORTED:
+        raise KernelError(f"{what}: the kernel refuses these sizes or types")
+    raise KernelError(f"{what}: CUDA error {code} ({torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+
+
+# ---- kernel choice --------------------------------------------------------------------
+
+_forced = {"gemm": None, "attention": None}
+
+
+@contextlib.contextmanager
+def force(gemm: Optional[str] = None, attention: Optional[str] = None):
+    """Pins the kernel family inside the block: gemm in {'generic','tc','smallm'},
+    attention in {'generic','flash'}.  A pinned kernel that refuses the shape raises."""
+    old = dict(_forced)
+    if gemm is not None:
+        _forced["gemm"] = gemm
+    if attention is not None:
+        _forced["attention"] = attention
+    try:
+        yield
+    finally:
+        _forced.update(old)
+
+
+# ---- embedding ------------------------------------------------------------------------
+
+
+def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[token_ids[t], :] widened to float32."""
+    _need(table, "table", dims=2)
+    _need(token_ids, "token_ids", torch.int32, 1)
+    _need(out, "out", torch.float32, 2)
+    n, d = out.shape
+    if token_ids.shape[0] != n or table.shape[1] != d:
+        raise KernelError(f"embedding: out {tuple(out.shape)} does not fit ids {tuple(token_ids.shape)} and table {tuple(table.shape)}")
+    lib = build.load("elementwise")
+    _check(lib.hk_embedding(_ptr(table), _dt(table), _ptr(token_ids), _ptr(out), n, d, table.shape[0], _stream()),
+           "embedding")
+
+
+# ---- rms norm -------------------------------------------------------------------------
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = x[rows[r] or r, :] * rsqrt(mean(x^2) + eps) * weight  (x, weight float32)."""
+    _need(x, "x", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    _need(out, "out", dims=2)
+    d = x.shape[1]
+    n_out = out.shape[0]
+    if weight.shape[0] != d or out.shape[1] != d:
+        raise KernelError("rms_norm: widths of x, weight and out differ")
+    if rows is None:
+        if n_out != x.shape[0]:
+            raise KernelError("rms_norm: out has other rows than x")
+    else:
+        _need(rows, "rows", torch.int32, 1)
+        if rows.shape[0] < n_out:
+            raise KernelError("rms_norm: fewer row indices than output rows")
+    lib = build.load("elementwise")
+    _check(lib.hk_rms_norm(_ptr(x), _ptr(weight), _ptr(rows), _ptr(out), _dt(out), n_out, d,
+                           ctypes.c_float(eps), _stream()), "rms_norm")
+
+
+# ---- swiglu ---------------------------------------------------------------------------
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, F + j]  (gate_up float32 [n, 2F])."""
+    _need(gate_up, "gate_up", torch.float32, 2)
+    _need(out, "out", dims=2)
+    n, f = out.shape
+    if gate_up.shape[0] != n or gate_up.shape[1] != 2 * f:
+        raise KernelError("swiglu: gate_up must be [n, 2F] for out [n, F]")
+    lib = build.load("elementwise")
+    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, _stream()), "swiglu")
+
+
+# ---- per-head norm + rotation + cache write ---------------------------------------------
+
+
+def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_dim, positions,
+                          slot_of_token, block_table, k_pages, v_pages, n_heads, n_kv_heads, head_dim,
+                          page_tokens, write_kv=True) -> None:
+    """Splits the fused projection qkv[n, (H+2G)*hd] (float32): q heads are normalised (if
+    q_weight), rotated (if rotary_dim > 0) and stored to q_out[n, H*hd]; k heads likewise and
+    stored, with the v heads, into the token's cache page [page, G, page_tokens, hd]."""
+    _need(qkv, "qkv", torch.float32, 2)
+    _need(q_out, "q_out", dims=2)
+    n = qkv.shape[0]
+    H, G, hd = n_heads, n_kv_heads, head_dim
+    if qkv.shape[1] != (H + 2 * G) * hd or tuple(q_out.shape) != (n, H * hd):
+        raise KernelError("qk_norm_rope_kv_write: qkv or q_out has the wrong shape")
+    if head_dim > 256:
+        raise KernelError(f"qk_norm_rope_kv_write: head_dim {head_dim} is above 256")
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _need(w, name, torch.float32, 1)
+            if w.shape[0] != hd:
+                raise KernelError(f"{name} must have head_dim entries")
+    if rotary_dim > 0:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape or rotary_dim % 2 or rotary_dim > hd:
+            raise KernelError("rotation tables must be [positions, rotary_dim/2]")
+    _need(positions, "positions", torch.int32, 1)
+    _need(slot_of_token, "slot_of_token", torch.int32, 1)
+    if write_kv:
+        _need(block_table, "block_table", torch.int32, 2)
+        _need(k_pages, "k_pages", q_out.dtype, 4)
+        _need(v_pages, "v_pages", q_out.dtype, 4)
+        if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or k_pages.shape != v_pages.shape:
+            raise KernelError("cache pages must be [pages, G, page_tokens, head_dim]")
+    lib = build.load("elementwise")
+    _check(lib.hk_qk_norm_rope_kv_write(
+        _ptr(qkv), _ptr(q_out), _dt(q_out), _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps),
+        _ptr(cos if rotary_dim > 0 else None), _ptr(sin if rotary_dim > 0 else None), int(rotary_dim),
+        _ptr(positions), _ptr(slot_of_token), _ptr(block_table if write_kv else None),
+        int(block_table.shape[1]) if write_kv else 0, _ptr(k_pages if write_kv else None),
+        _ptr(v_pages if write_kv else None), n, H, G, hd, int(page_tokens), 1 if write_kv else 0, _stream()),
+        "qk_norm_rope_kv_write")
+
+
+# ---- matrix product -------------------------------------------------------------------
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M, N] (float32) = a[M, K] @ w[N, K]^T (+ out when `accumulate`).
+    a and w share a type: float32 (plain FMA) or bfloat16 (fp32 accumulation)."""
+    _need(a, "a", dims=2)
+    _need(w, "w", a.dtype, 2)
+    _need(out, "out", torch.float32, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    choice = _forced["gemm"]
+    if a.dtype == torch.bfloat16 and choice != "generic":
+        from . import gemm_fast
+        if gemm_fast.run(a, w, out, accumulate, choice):
+            return
+        if choice is not None:
+            raise KernelError(f"gemm: the '{choice}' kernel refuses M={M} N={N} K={K}")
+    lib = build.load("gemm_generic")
+    _check(lib.hk_gemm_generic(_ptr(a), _ptr(w), _dt(a), _ptr(out), M, N, K, ctypes.c_longlong(K),
+                               ctypes.c_longlong(K), ctypes.c_longlong(N), 1 if accumulate else 0, _stream()),
+           "gemm")
+
+
+# ---- attention ------------------------------------------------------------------------
+
+
+def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, out, n_heads, n_kv_heads,
+                    head_dim, page_tokens, window: int, scale: float, plan=None) -> None:
+    """out[t, h, :] = softmax_j(scale * q[t, h] . k[j]) v[j] over the keys j in
+    [max(0, p - window + 1), p] (all of [0, p] when window <= 0) of the token's request, read
+    through its block-table row; p = positions[t].  `plan` carries the per-request tiling the
+    flash kernel wants; without it (or for sizes it refuses) the generic kernel runs."""
+    _need(q, "q", dims=2)
+    _need(out, "out", q.dtype, 2)
+    _need(k_pages, "k_pages", q.dtype, 4)
+    _need(v_pages, "v_pages", q.dtype, 4)
+    _need(block_table, "block_table", torch.int32, 2)
+    _need(positions, "positions", torch.int32, 1)
+    _need(slot_of_token, "slot_of_token", torch.int32, 1)
+    n = q.shape[0]
+    H, G, hd = n_heads, n_kv_heads, head_dim
+    if tuple(q.shape) != (n, H * hd) or out.shape != q.shape:
+        raise KernelError("paged_attention: q and out must be [n, H*head_dim]")
+    if tuple(k_pages.shape[1:]) != (G, page_tokens, hd) or k_pages.shape != v_pages.shape:
+        raise KernelError("paged_attention: cache pages must be [pages, G, page_tokens, head_dim]")
+    if H % G != 0:
+        raise KernelError(f"paged_attention: {H} heads are not a multiple of {G} groups")
+    if hd > 256:
+        raise KernelError(f"paged_attention: head_dim {hd} is above 256")
+    choice = _forced["attention"]
+    if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None:
+        from . import attention_fast
+        if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan):
+            return
+        if choice is not None:
+            raise KernelError(f"paged_attention: the '{choice}' kernel refuses head_dim={hd} page_tokens={page_tokens}")
+    lib = build.load("attention_generic")
+    _check(lib.hk_attention_generic(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _dt(q), _ptr(block_table), int(block_table.shape[1]),
+        _ptr(positions), _ptr(slot_of_token), _ptr(out), n, H, G, hd, int(page_tokens), int(window),
+        ctypes.c_float(scale), _stream()), "paged_attention")

@@ -1,0 +1,41 @@
+"""What a step hands to the parts: the flattened rows of the batch and who they belong to."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..parts.base import Precision
+
+
+@dataclass
+class StepContext:
+    """One step's batch, flattened.  Row t is a token; rows of one request are consecutive and
+    in increasing position (the reference's rule for items that share a cache:
+    src/engine/kv.zig:22-24).
+
+    Device tensors (int32): token_ids[n], positions[n], slot_of_token[n].
+    Host lists, one entry per request of the step, in batch order: slots, q_starts (first row),
+    q_lens (rows), start_positions (position of the first row).
+    """
+    precision: Precision
+    n_tokens: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    slot_of_token: torch.Tensor
+    slots: List[int]
+    q_starts: List[int]
+    q_lens: List[int]
+    start_positions: List[int]
+    plans: Dict[int, object] = field(default_factory=dict)
+    plan_builder: Optional[object] = None
+
+    def attention_plan(self, page_tokens: int):
+        """The tiling of this batch for the flash attention kernel (built once per step and
+        page size); None sends attention to the generic kernel."""
+        if self.plan_builder is None:
+            return None
+        if page_tokens not in self.plans:
+            self.plans[page_tokens] = self.plan_builder(self, page_tokens)
+        return self.plans[page_tokens]

@@ -1,0 +1,214 @@
+"""The engine: a model on one GPU, its cache, and the one step function.
+
+`Engine.step(entries)` takes a batch of (request, its next tokens, wanted places): portions
+of prompts beside single decoded tokens, cut anywhere.  It runs only those tokens, as one
+batch, over the cache that earlier steps left, and returns the float32 logits at the wanted
+places.  This is the reference's `forwardItems` + `logitsMany`
+(src/engine/model.zig:292-343): a flat list of items mixing sequences, K/V of the whole
+batch written before attention (src/engine/cpu_backend.zig:290-295), logits only for the
+asked rows (cpu_backend.zig:342-357).  Errors (`BatchTooLarge`, `ContextFull`,
+`TokenOutOfRange`, `OutOfPages`; cf. src/engine/model.zig:53-59,296-300) are raised before
+anything changes, and the engine stays usable (tests/test_engine.zig:189-203 holds the
+reference to the same).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.device import PagedCache
+from ..cache.pages import CacheError, ContextFull, OutOfPages
+from ..config import ModelConfig, load_config, resolve_architecture
+from ..parts.base import Precision
+from ..weights.loader import load_tensors, random_tensors
+from .context import StepContext
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+class BatchTooLarge(EngineError):
+    pass
+
+
+class TokenOutOfRange(EngineError):
+    pass
+
+
+class UnknownRequest(EngineError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    """A request's share of a step: its next tokens and the places among them (indices into
+    `tokens`) whose logits are wanted."""
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+_DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, torch.bfloat16: torch.bfloat16,
+    "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32, torch.float32: torch.float32,
+}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r} is not 'bfloat16' or 'float32'") from None
+
+
+def _resolve_device(device) -> torch.device:
+    if not torch.cuda.is_available():
+        raise EngineError("no CUDA device: this engine runs on a GPU only (there is no CPU path)")
+    dev = torch.device("cuda", int(device))
+    torch.cuda.set_device(dev)
+    return dev
+
+
+class Engine:
+    """A model bound to `cuda:device`, with a page pool for `max_tokens` cached tokens."""
+
+    def __init__(self, model_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
+                 random_seed: Optional[int] = None, random_std: Optional[float] = None,
+                 random_norm_std: float = 0.05, dtype="bfloat16", max_tokens: int = 8192,
+                 page_tokens: int = 16, max_requests: int = 8, max_context: Optional[int] = None,
+                 max_batch_tokens: int = 8192, device: int = 0):
+        self.device = _resolve_device(device)
+        self.precision = Precision(parse_dtype(dtype), self.device)
+        if config is None:
+            if model_dir is None:
+                raise ValueError("give a model folder or a configuration")
+            config = load_config(model_dir)
+        self.config = config
+        _, build_model = resolve_architecture(config.architecture)
+        if max_tokens % page_tokens:
+            max_tokens += page_tokens - max_tokens % page_tokens
+        limit = getattr(config, "max_position_embeddings", None) or max_tokens
+        self.max_context = int(max_context) if max_context else int(min(limit, max_tokens))
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.model = build_model(config, self.max_context)
+        specs = self.model.param_specs()
+        with torch.no_grad():
+            if random_seed is not None:
+                std = random_std if random_std is not None else float(getattr(config, "initializer_range", 0.02))
+                tensors = random_tensors(specs, random_seed, std, random_norm_std, self.device,
+                                         dtype_of=lambda s: self.precision.working_dtype(s.kind))
+            else:
+                tensors = load_tensors(model_dir, specs, self.precision)
+            self.model.bind(tensors, self.precision)
+            del tensors
+        self.cache = PagedCache(self.model.cache_specs(), self.precision, page_tokens, max_tokens // page_tokens,
+                                max_requests, self.max_context)
+        self.vocab = self.model.vocab
+        self._requests: Dict[Hashable, int] = {}
+        self.plan_builder = None
+        self.steps_run = 0
+
+    # -- requests ----------------------------------------------------------------------------
+    def open_request(self, request: Hashable) -> None:
+        if request in self._requests:
+            raise EngineError(f"request {request!r} is already open")
+        self._requests[request] = self.cache.open()
+
+    def close_request(self, request: Hashable) -> None:
+        slot = self._requests.pop(request, None)
+        if slot is None:
+            raise UnknownRequest(f"request {request!r} is not open")
+        self.cache.close(slot)
+
+    def has_request(self, request: Hashable) -> bool:
+        return request in self._requests
+
+    def request_length(self, request: Hashable) -> int:
+        return int(self.cache.books.length[self._slot(request)])
+
+    def _slot(self, request: Hashable) -> int:
+        try:
+            return self._requests[request]
+        except KeyError:
+            raise UnknownRequest(f"request {request!r} is not open") from None
+
+    def free_pages(self) -> List[int]:
+        return self.cache.books.free_pages()
+
+    # -- the step function -------------------------------------------------------------------
+    def check_step(self, entries: Sequence[StepEntry]) -> None:
+        """Raises what `step` would raise, changing nothing."""
+        books = self.cache.books
+        total = 0
+        seen = set()
+        take = [0] * len(books.groups)
+        for e in entries:
+            slot = self._slot(e.request)
+            if e.request in seen:
+                raise EngineError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            n = len(e.tokens)
+            if n < 1:
+                raise EngineError(f"request {e.request!r} brings no tokens")
+            for tok in e.tokens:
+                if not 0 <= int(tok) < self.vocab:
+                    raise TokenOutOfRange(f"token id {tok} is outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise EngineError(f"wanted place {w} is outside the {n} tokens of request {e.request!r}")
+            if int(books.length[slot]) + n > books.max_context:
+                raise ContextFull(
+                    f"request {e.request!r} would reach {int(books.length[slot]) + n} tokens; the context holds {books.max_context}")
+            total += n
+            # pages the window has passed come back before any are taken
+            passed = [len(books._passed(g, slot, int(books.length[slot]))) for g in books.groups]
+            for gi, k in enumerate(books.pages_to_take(slot, n)):
+                take[gi] += k - passed[gi]
+        if total > self.max_batch_tokens:
+            raise BatchTooLarge(f"{total} tokens in one step; the engine takes {self.max_batch_tokens}")
+        for gi, k in enumerate(take):
+            if k > books.groups[gi].pool.free_count:
+                raise OutOfPages(f"the step needs {k} more pages in group {gi}; {books.groups[gi].pool.free_count} are free")
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch.  Returns float32 logits [wanted, vocab] on the device, in the order
+        of the entries and of their `want`, or None when nothing is wanted."""
+        if not entries:
+            return None
+        self.check_step(entries)
+        books = self.cache.books
+        slots = [self._slot(e.request) for e in entries]
+        for s in slots:
+            books.release_passed(s)
+        starts = [int(books.length[s]) for s in slots]
+        for s, e in zip(slots, entries):
+            books.extend(s, len(e.tokens))
+        self.cache.sync_tables()
+
+        n = sum(len(e.tokens) for e in entries)
+        meta = np.empty((3, n), dtype=np.int32)
+        q_starts, q_lens, rows = [], [], []
+        r = 0
+        for s, st, e in zip(slots, starts, entries):
+            m = len(e.tokens)
+            meta[0, r:r + m] = np.asarray(e.tokens, dtype=np.int32)
+            meta[1, r:r + m] = np.arange(st, st + m, dtype=np.int32)
+            meta[2, r:r + m] = s
+            rows.extend(r + int(w) for w in e.want)
+            q_starts.append(r)
+            q_lens.append(m)
+            r += m
+        meta_dev = torch.from_numpy(meta).to(self.device)
+        ctx = StepContext(self.precision, n, meta_dev[0], meta_dev[1], meta_dev[2], slots, q_starts, q_lens,
+                          starts, plan_builder=self.plan_builder)
+        x = self.model.forward(ctx, self.cache.layers)
+        self.steps_run += 1
+        if not rows:
+            return None
+        rows_dev = torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(self.device)
+        return self.model.head.forward(x, rows_dev, len(rows), ctx)

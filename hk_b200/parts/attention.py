@@ -1,0 +1,98 @@
+"""Grouped-query attention over a paged cache, as a mixer part.
+
+Steps, in the reference's order (src/engine/cpu_backend.zig:266-304):
+  q, k, v = xb Wq^T, xb Wk^T, xb Wv^T   (one fused product; no bias: src/engine/config.zig:313)
+  per-head RMS norm of q and of k with a weight [head_dim] shared by the heads, before the
+  rotation (src/engine/ops.zig:32-38, src/kernels_impl.zig:55-66) - optional here
+  rotate-half rotation of q and k by position (src/engine/ops.zig:176-181) - optional here
+  the step's k and v go to the cache before any score is taken (cpu_backend.zig:290-295)
+  scores scale * q . k_j over the visible keys, softmax in float32, weighted values
+  (src/engine/attention.zig:45-103), q head h reading kv head h // (H/G) (attention.zig:56)
+  residual += att Wo^T (cpu_backend.zig:303-304)
+
+Sizes, the norm's eps, the position encoding, the window and the scale are parameters.  The
+reference's attention has no window (src/engine/config.zig:271-279 refuses one); `window=w`
+limits the keys of position p to (p - w, p] and lets the cache give pages back.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import KVCacheSpec, MATRIX, VECTOR, ParamSpec, Part, Precision, register_part
+from .position import RotaryEmbedding
+
+
+class GQAAttention(Part):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
+                 qk_norm_eps: Optional[float] = None, position: Optional[RotaryEmbedding] = None,
+                 window: Optional[int] = None, scale: Optional[float] = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+        if head_dim > 256 or head_dim < 2:
+            raise ValueError(f"head_dim {head_dim} is outside 2..256")
+        if position is not None and position.rotary_dim > head_dim:
+            raise ValueError("the rotary width exceeds head_dim")
+        self.hidden, self.H, self.G, self.hd = hidden, n_heads, n_kv_heads, head_dim
+        self.prefix = prefix
+        self.qk_norm_eps = qk_norm_eps
+        self.position = position
+        self.window = window
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    # -- declaration ---------------------------------------------------------------------
+    def children(self):
+        return (self.position,) if self.position is not None else ()
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, H, G, hd, d = self.prefix, self.H, self.G, self.hd, self.hidden
+        specs = {
+            p + "q_proj.weight": ParamSpec((H * hd, d), MATRIX),
+            p + "k_proj.weight": ParamSpec((G * hd, d), MATRIX),
+            p + "v_proj.weight": ParamSpec((G * hd, d), MATRIX),
+            p + "o_proj.weight": ParamSpec((d, H * hd), MATRIX),
+        }
+        if self.qk_norm_eps is not None:
+            specs[p + "q_norm.weight"] = ParamSpec((hd,), VECTOR, "one_plus_normal")
+            specs[p + "k_norm.weight"] = ParamSpec((hd,), VECTOR, "one_plus_normal")
+        return specs
+
+    def cache_spec(self):
+        return KVCacheSpec(self.G, self.hd, self.window)
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p = self.prefix
+        self.w_qkv = torch.cat([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"],
+                                tensors[p + "v_proj.weight"]], dim=0).contiguous()
+        self.w_o = tensors[p + "o_proj.weight"]
+        if self.qk_norm_eps is not None:
+            self.q_norm = tensors[p + "q_norm.weight"]
+            self.k_norm = tensors[p + "k_norm.weight"]
+
+    # -- one step ------------------------------------------------------------------------
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True) -> None:
+        n = xb.shape[0]
+        H, G, hd = self.H, self.G, self.hd
+        qkv = torch.empty((n, (H + 2 * G) * hd), dtype=torch.float32, device=xb.device)
+        ops.gemm(xb, self.w_qkv, qkv)
+        q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)
+        cos = sin = None
+        rot = 0
+        if self.position is not None:
+            cos, sin, rot = self.position.tables()
+        ops.qk_norm_rope_kv_write(
+            qkv, q, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, cos, sin, rot, ctx.positions,
+            ctx.slot_of_token, cache.block_table, cache.k_pages, cache.v_pages, H, G, hd, cache.page_tokens,
+            write_kv=write_cache)
+        att = torch.empty_like(q)
+        ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
+                            att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
+                            plan=ctx.attention_plan(cache.page_tokens))
+        ops.gemm(att, self.w_o, residual, accumulate=True)
+
+
+register_part("mixer", "gqa_attention", GQAAttention)

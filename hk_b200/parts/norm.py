@@ -1,0 +1,30 @@
+"""RMS norm: out = x * rsqrt(mean(x^2) + eps) * weight, in float32
+(src/engine/ops.zig:10-29).  Width, eps and the tensor name are parameters."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import VECTOR, ParamSpec, Part, Precision, register_part
+
+
+class RMSNorm(Part):
+    def __init__(self, width: int, eps: float, weight_name: str):
+        self.width = width
+        self.eps = float(eps)
+        self.weight_name = weight_name
+        self.weight: Optional[torch.Tensor] = None
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.width,), VECTOR, "one_plus_normal")}
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        self.weight = tensors[self.weight_name]
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        ops.rms_norm(x, self.weight, self.eps, out, rows)
+
+
+register_part("norm", "rmsnorm", RMSNorm)
