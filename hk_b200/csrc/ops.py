@@ -244,3 +244,51 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _dt(q), _ptr(block_table), int(block_table.shape[1]),
         _ptr(positions), _ptr(slot_of_token), _ptr(out), n, H, G, hd, int(page_tokens), int(window),
         ctypes.c_float(scale), _stream()), "paged_attention")
+
+
+# ---- sampling -------------------------------------------------------------------------
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of logits[r, :] (float32)."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(out, "out", torch.int32, 1)
+    if out.shape[0] != logits.shape[0]:
+        raise KernelError("argmax: one output per row")
+    lib = build.load("sampling")
+    _check(lib.hk_argmax(_ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax")
+
+
+def adjust_logits(logits, offsets, ids, counts, bias, repeat_penalty, freq_penalty, presence_penalty) -> None:
+    """Applies repetition, frequency and presence penalties and logit biases in place: entries
+    offsets[r]..offsets[r+1] of (ids, counts, bias) belong to row r."""
+    _need(logits, "logits", torch.float32, 2)
+    rows = logits.shape[0]
+    for name, t, dt, n in (("offsets", offsets, torch.int32, rows + 1), ("ids", ids, torch.int32, None),
+                           ("counts", counts, torch.int32, ids.shape[0]), ("bias", bias, torch.float32, ids.shape[0]),
+                           ("repeat_penalty", repeat_penalty, torch.float32, rows),
+                           ("freq_penalty", freq_penalty, torch.float32, rows),
+                           ("presence_penalty", presence_penalty, torch.float32, rows)):
+        _need(t, name, dt, 1)
+        if n is not None and t.shape[0] != n:
+            raise KernelError(f"adjust_logits: {name} has {t.shape[0]} entries, expected {n}")
+    lib = build.load("sampling")
+    _check(lib.hk_adjust_logits(_ptr(logits), rows, logits.shape[1], _ptr(offsets), _ptr(ids), _ptr(counts), _ptr(bias),
+                                _ptr(repeat_penalty), _ptr(freq_penalty), _ptr(presence_penalty), _stream()),
+           "adjust_logits")
+
+
+def sample(logits, temperature, top_k, top_p, min_p, seeds, counters, out) -> None:
+    """One token per row by the chain top-k -> top-p -> min-p -> temperature -> draw; rows with
+    temperature <= 0 take the first maximum.  seeds and counters are int64 per row."""
+    _need(logits, "logits", torch.float32, 2)
+    rows = logits.shape[0]
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32),
+                        ("seeds", seeds, torch.int64), ("counters", counters, torch.int64), ("out", out, torch.int32)):
+        _need(t, name, dt, 1)
+        if t.shape[0] != rows:
+            raise KernelError(f"sample: {name} must have one entry per row")
+    lib = build.load("sampling")
+    _check(lib.hk_sample(_ptr(logits), rows, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p),
+                         _ptr(seeds), _ptr(counters), _ptr(out), _stream()), "sample")

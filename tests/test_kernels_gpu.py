@@ -1,0 +1,253 @@
+"""Each CUDA kernel alone against its plain reference (tests/ref_ops.py), at sizes other than
+the engine tests': odd widths, head sizes in steps of 16, any number of heads and groups.
+Tolerances: float32 kernels within accumulated float32 rounding of the float64 reference;
+bfloat16 storage within half a unit in the last place of the result plus the same; matrix
+products scaled by sum |a||b| (the reference's own rule, tests/test_cuda.zig:374-378)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import ref_ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+def ops():
+    from hk_b200.csrc import ops as o
+    return o
+
+
+def close(got, want, dtype, atol=1e-5, rtol=1e-5):
+    got = got.double().cpu()
+    want = want.double().cpu()
+    if dtype == torch.bfloat16:
+        rtol, atol = max(rtol, 2 ** -8), max(atol, 1e-5)
+    bad = (got - want).abs() > atol + rtol * want.abs()
+    assert not bad.any(), f"{int(bad.sum())} of {bad.numel()} differ; worst {(got - want).abs().max():.3g} at {tuple(np.unravel_index(int((got - want).abs().argmax()), got.shape))}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("n,d,vocab", [(1, 8, 3), (37, 72, 333), (5, 4100, 17)])
+def test_embedding(dtype, n, d, vocab):
+    g = torch.Generator().manual_seed(n + d)
+    table = torch.randn(vocab, d, generator=g).to(dtype)
+    ids = torch.randint(0, vocab, (n,), generator=g, dtype=torch.int32)
+    out = torch.empty(n, d, dtype=torch.float32, device=DEV)
+    ops().embedding(table.to(DEV), ids.to(DEV), out)
+    assert torch.equal(out.cpu(), ref_ops.embedding(table, ids))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("n,d,eps", [(1, 16, 1e-6), (19, 72, 1e-5), (3, 4104, 3e-6), (130, 96, 0.0)])
+def test_rms_norm(dtype, n, d, eps):
+    g = torch.Generator().manual_seed(d)
+    x = torch.randn(n, d, generator=g) * 3 + 0.5
+    w = 1 + 0.1 * torch.randn(d, generator=g)
+    out = torch.empty(n, d, dtype=dtype, device=DEV)
+    ops().rms_norm(x.to(DEV), w.to(DEV), eps, out)
+    close(out, ref_ops.rms_norm(x, w, eps), dtype)
+    rows = torch.tensor([n - 1, 0, n // 2], dtype=torch.int32)
+    out = torch.empty(3, d, dtype=dtype, device=DEV)
+    ops().rms_norm(x.to(DEV), w.to(DEV), eps, out, rows.to(DEV))
+    close(out, ref_ops.rms_norm(x, w, eps, rows), dtype)
+
+
+def test_rms_norm_reference_fact():
+    # src/engine/ops.zig:227-234
+    out = torch.empty(1, 4, dtype=torch.float32, device=DEV)
+    ops().rms_norm(torch.tensor([[2.0, -2, 2, -2]], device=DEV), torch.ones(4, device=DEV), 0.0, out)
+    assert torch.allclose(out.cpu(), torch.tensor([[1.0, -1, 1, -1]]), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("n,f", [(1, 1), (7, 200), (33, 1111)])
+def test_swiglu(dtype, n, f):
+    gu = torch.randn(n, 2 * f, generator=torch.Generator().manual_seed(f)) * 4
+    out = torch.empty(n, f, dtype=dtype, device=DEV)
+    ops().swiglu(gu.to(DEV), out)
+    close(out, ref_ops.swiglu(gu), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (13, 300, 256), (65, 129, 1000), (2, 1000, 72), (128, 64, 64)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_generic(dtype, m, n, k, accumulate):
+    g = torch.Generator().manual_seed(m * n + k)
+    a = torch.randn(m, k, generator=g).to(dtype)
+    w = torch.randn(n, k, generator=g).to(dtype)
+    out0 = torch.randn(m, n, generator=g)
+    out = out0.clone().to(DEV)
+    with ops().force(gemm="generic"):
+        ops().gemm(a.to(DEV), w.to(DEV), out, accumulate=accumulate)
+    want = ref_ops.gemm(a, w, out0 if accumulate else None)
+    bound = a.double().abs() @ w.double().abs().T          # sum |a||b|
+    err = (out.double().cpu() - want).abs()
+    assert (err <= 1e-6 * bound + 1e-6 * want.abs() + 1e-7).all(), f"worst {err.max():.3g}"
+
+
+def make_paged(rng, n_slots, lens, G, hd, pt, dtype, extra_pages=3):
+    """Random cache contents in scattered pages; returns (k_pages, v_pages, block_table, k, v) with
+    k, v the dense float64 [slot][len, G, hd] contents (already rounded to `dtype`)."""
+    max_pages = max(-(-l // pt) for l in lens) + 1
+    total = sum(-(-l // pt) for l in lens) + extra_pages
+    perm = rng.permutation(total)
+    bt = np.full((n_slots, max_pages), -1, dtype=np.int32)
+    k_pages = torch.zeros(total, G, pt, hd, dtype=dtype)
+    v_pages = torch.zeros(total, G, pt, hd, dtype=dtype)
+    dense_k, dense_v = [], []
+    nxt = 0
+    for s, l in enumerate(lens):
+        k = torch.from_numpy(rng.standard_normal((l, G, hd))).to(dtype)
+        v = torch.from_numpy(rng.standard_normal((l, G, hd))).to(dtype)
+        dense_k.append(k.double())
+        dense_v.append(v.double())
+        for i in range(-(-l // pt)):
+            page = int(perm[nxt])
+            nxt += 1
+            bt[s, i] = page
+            seg = slice(i * pt, min(l, (i + 1) * pt))
+            k_pages[page, :, :seg.stop - seg.start] = k[seg].transpose(0, 1)
+            v_pages[page, :, :seg.stop - seg.start] = v[seg].transpose(0, 1)
+    return k_pages, v_pages, torch.from_numpy(bt), dense_k, dense_v
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,hd,pt,rot,norm", [
+    (4, 2, 16, 4, 16, True), (5, 1, 48, 16, 24, True), (6, 3, 80, 8, 80, False), (8, 8, 128, 16, 128, True),
+    (3, 1, 256, 32, 64, True), (2, 2, 32, 1, 0, False)])
+def test_qk_norm_rope_kv_write(dtype, H, G, hd, pt, rot, norm):
+    rng = np.random.default_rng(H * hd + pt)
+    lens = [9, 30, 17]
+    k_pages, v_pages, bt, _, _ = make_paged(rng, 3, lens, G, hd, pt, dtype)
+    k_pages.zero_()
+    v_pages.zero_()
+    # tokens: a portion of slot 1 (positions 12..29), one token of slot 0 (position 8), three of slot 2
+    slot = torch.tensor([1] * 18 + [0] + [2] * 3, dtype=torch.int32)
+    pos = torch.tensor(list(range(12, 30)) + [8] + [14, 15, 16], dtype=torch.int32)
+    n = slot.numel()
+    qkv = torch.from_numpy(rng.standard_normal((n, (H + 2 * G) * hd))).float() * 2
+    qw = (1 + 0.2 * torch.from_numpy(rng.standard_normal(hd))).float() if norm else None
+    kw = (1 + 0.2 * torch.from_numpy(rng.standard_normal(hd))).float() if norm else None
+    eps = 1e-5
+    half = max(rot // 2, 1)
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * torch.from_numpy(rng.uniform(0.001, 1.0, half))[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    q_out = torch.empty(n, H * hd, dtype=dtype, device=DEV)
+    kp, vp = k_pages.to(DEV), v_pages.to(DEV)
+    d = lambda t: None if t is None else t.to(DEV)
+    ops().qk_norm_rope_kv_write(qkv.to(DEV), q_out, d(qw), d(kw), eps, d(cos) if rot else None, d(sin) if rot else None,
+                                rot, pos.to(DEV), slot.to(DEV), bt.to(DEV), kp, vp, H, G, hd, pt)
+    q, k, v = ref_ops.qk_norm_rope(qkv, qw, kw, eps, cos, sin, rot, pos, H, G, hd)
+    close(q_out, q.reshape(n, H * hd), dtype)
+    rk, rv = torch.zeros_like(k_pages, dtype=torch.float64), torch.zeros_like(v_pages, dtype=torch.float64)
+    ref_ops.write_pages(k, v, rk, rv, bt, slot, pos, pt)
+    close(kp, rk, dtype)        # untouched places must still be zero
+    close(vp, rv, dtype)
+    # a layer that reads another layer's cache writes nothing
+    kp2, vp2 = torch.zeros_like(kp), torch.zeros_like(vp)
+    q2 = torch.empty_like(q_out)
+    ops().qk_norm_rope_kv_write(qkv.to(DEV), q2, d(qw), d(kw), eps, d(cos) if rot else None, d(sin) if rot else None,
+                                rot, pos.to(DEV), slot.to(DEV), bt.to(DEV), kp2, vp2, H, G, hd, pt, write_kv=False)
+    assert torch.equal(q2, q_out) and not kp2.any() and not vp2.any()
+
+
+def test_rotation_reference_fact():
+    # src/engine/ops.zig:236-252: 90 degrees in the half-split pairing: [1,0,0,1] -> [0,-1,1,0]
+    qkv = torch.tensor([[1.0, 0, 0, 1] + [0.0] * 8], device=DEV)
+    q_out = torch.empty(1, 4, dtype=torch.float32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kp = torch.zeros(1, 1, 1, 4, device=DEV)
+    ops().qk_norm_rope_kv_write(qkv, q_out, None, None, 0.0, torch.zeros(1, 2, device=DEV), torch.ones(1, 2, device=DEV),
+                                4, z, z, torch.zeros(1, 1, dtype=torch.int32, device=DEV), kp, kp.clone(), 1, 1, 4, 1)
+    assert torch.allclose(q_out.cpu(), torch.tensor([[0.0, -1, 1, 0]]), atol=1e-6)
+
+
+ATT_SHAPES = [(4, 2, 16, 4), (5, 1, 48, 16), (6, 2, 80, 8), (8, 2, 128, 16), (3, 3, 256, 16), (7, 7, 32, 32), (8, 1, 64, 16),
+              (2, 1, 112, 16)]
+
+
+def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=None):
+    """q_spans: per slot (first position, count) of the query rows; the cache holds lens[s] keys."""
+    rng = np.random.default_rng(H * 1000 + hd + pt + window)
+    k_pages, v_pages, bt, dk, dv = make_paged(rng, len(lens), lens, G, hd, pt, dtype)
+    slot, pos = [], []
+    for s, (p0, c) in enumerate(q_spans):
+        slot += [s] * c
+        pos += list(range(p0, p0 + c))
+    n = len(slot)
+    q = torch.from_numpy(rng.standard_normal((n, H * hd))).to(dtype)
+    if spike is not None:
+        # make one far key dominate one query row: the output must be that key's value
+        row, s, j, g = spike
+        kk = dk[s][j, g].clone()
+        k_page = int(bt[s, j // pt])
+        big = (kk / kk.norm() * 30).to(dtype)
+        k_pages[k_page, g, j % pt] = big
+        dk[s][j, g] = big.double()
+        group = H // G
+        for h in range(g * group, (g + 1) * group):
+            q[row, h * hd:(h + 1) * hd] = (big.double() * (math.sqrt(hd) * 2)).to(dtype) / 30 * 3
+    slot_t, pos_t = torch.tensor(slot, dtype=torch.int32), torch.tensor(pos, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.empty(n, H * hd, dtype=dtype, device=DEV)
+    plan = None
+    with ops().force(attention=kernel):
+        ops().paged_attention(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), bt.to(DEV), pos_t.to(DEV), slot_t.to(DEV), out,
+                              H, G, hd, pt, window, scale, plan=plan)
+    want = ref_ops.paged_attention(q, k_pages, v_pages, bt, pos_t, slot_t, H, G, hd, pt, window, scale)
+    return out, want, (q, dk, dv, slot, pos)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,hd,pt", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 13])
+def test_attention_generic_mixed_batch(dtype, H, G, hd, pt, window):
+    # slot 0: a decode token at position 299 of 300; slot 1: a portion 37..69 of 70; slot 2: the first 5 tokens
+    out, want, _ = attention_case("generic", dtype, H, G, hd, pt, window, [300, 70, 5], [(299, 1), (37, 33), (0, 5)])
+    close(out, want, dtype, atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("j", [0, 15, 16, 17, 255, 256, 481])
+def test_attention_generic_finds_a_far_key(dtype, j):
+    # 500 keys; key j (a page's first, last, or middle place) is made to dominate the decode query
+    H, G, hd, pt = 4, 2, 64, 16
+    out, want, (q, dk, dv, slot, pos) = attention_case("generic", dtype, H, G, hd, pt, 0, [500], [(499, 1)], spike=(0, 0, j, 1))
+    close(out, want, dtype, atol=2e-5, rtol=1e-4)
+    got = out.double().cpu().reshape(1, H, hd)
+    assert torch.allclose(got[0, 2], dv[0][j, 1], atol=0.05) and torch.allclose(got[0, 3], dv[0][j, 1], atol=0.05)
+    assert not torch.allclose(got[0, 0], dv[0][j, 1], atol=0.05)     # the other group did not see the spike
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_attention_generic_window_edge(dtype):
+    # window 20 at position 99 reads keys 80..99: a dominant key at 80 is seen, one at 79 is not
+    H, G, hd, pt = 2, 1, 32, 8
+    out, want, (_, _, dv, _, _) = attention_case("generic", dtype, H, G, hd, pt, 20, [100], [(99, 1)], spike=(0, 0, 80, 0))
+    close(out, want, dtype, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(out.double().cpu().reshape(H, hd)[0], dv[0][80, 0], atol=0.05)
+    out, want, (_, _, dv, _, _) = attention_case("generic", dtype, H, G, hd, pt, 20, [100], [(99, 1)], spike=(0, 0, 79, 0))
+    close(out, want, dtype, atol=2e-5, rtol=1e-4)
+    assert not torch.allclose(out.double().cpu().reshape(H, hd)[0], dv[0][79, 0], atol=0.2)
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    o = ops()
+    with pytest.raises(o.KernelError):
+        o.gemm(torch.zeros(2, 3, device=DEV), torch.zeros(4, 5, device=DEV), torch.zeros(2, 4, device=DEV))
+    with pytest.raises(o.KernelError):
+        o.rms_norm(torch.zeros(2, 8, device=DEV), torch.ones(4, device=DEV), 1e-6, torch.zeros(2, 8, device=DEV))
+    with pytest.raises(o.KernelError):
+        o.embedding(torch.zeros(4, 8), torch.zeros(2, dtype=torch.int32, device=DEV), torch.zeros(2, 8, device=DEV))
+    with pytest.raises(o.KernelError):
+        o.swiglu(torch.zeros(2, 7, device=DEV), torch.zeros(2, 3, device=DEV))
+    with pytest.raises(o.KernelError):       # head size above 256
+        z = torch.zeros(1, dtype=torch.int32, device=DEV)
+        o.paged_attention(torch.zeros(1, 272, device=DEV), torch.zeros(1, 1, 4, 272, device=DEV), torch.zeros(1, 1, 4, 272, device=DEV),
+                          torch.zeros(1, 1, dtype=torch.int32, device=DEV), z, z, torch.zeros(1, 272, device=DEV), 1, 1, 272, 4, 0, 1.0)

@@ -1,0 +1,309 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with
+state of its own that is registered, built and stepped without touching the package."""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+def tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-5)
+
+
+def bind_random(part, dtype, seed=0, std=0.05, norm_std=0.1):
+    """Random tensors for a part's declared parameters, bound on the GPU; returns float64 numpy copies
+    of exactly what the part computes with."""
+    from hk_b200.parts import Precision
+    from hk_b200.weights import random_tensors
+    prec = Precision(dtype, torch.device("cuda"))
+    tensors = random_tensors(part.param_specs(), seed, std, norm_std, "cuda", dtype_of=lambda s: prec.working_dtype(s.kind))
+    host = {k: v.double().cpu().numpy() for k, v in tensors.items()}
+    part.bind(tensors, prec)
+    return prec, host
+
+
+def make_ctx(prec, spans, cache=None, page_tokens=8):
+    """spans: [(slot, first position, count)]; extends `cache` (a PagedCache) accordingly."""
+    from hk_b200.engine.context import StepContext
+    slot, pos, q_starts, q_lens, starts, slots = [], [], [], [], [], []
+    for s, p0, c in spans:
+        q_starts.append(len(slot))
+        slot += [s] * c
+        pos += list(range(p0, p0 + c))
+        q_lens.append(c)
+        starts.append(p0)
+        slots.append(s)
+        if cache is not None:
+            assert int(cache.books.length[s]) == p0
+            cache.books.extend(s, c)
+    if cache is not None:
+        cache.sync_tables()
+    dev = prec.device
+    return StepContext(prec, len(slot), torch.zeros(len(slot), dtype=torch.int32, device=dev),
+                       torch.tensor(pos, dtype=torch.int32, device=dev), torch.tensor(slot, dtype=torch.int32, device=dev),
+                       slots, q_starts, q_lens, starts)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_rms_norm_part(dtype):
+    from hk_b200.parts import RMSNorm
+    part = RMSNorm(72, 3e-6, "n.weight")
+    prec, w = bind_random(part, dtype)
+    assert part.weight.dtype == torch.float32
+    x = torch.randn(11, 72, device="cuda") * 2
+    out = torch.empty(11, 72, dtype=dtype, device="cuda")
+    part.forward(x, out)
+    np.testing.assert_allclose(out.double().cpu().numpy(), P.rms_norm(x.double().cpu().numpy(), w["n.weight"], 3e-6), **tol(dtype))
+
+
+def test_rotary_tables_match_the_plain_angles():
+    from hk_b200.parts import Precision, RotaryEmbedding
+    part = RotaryEmbedding(1e6, 24, 300)
+    part.bind({}, Precision(torch.float32, torch.device("cuda")))
+    cos, sin, rot = part.tables()
+    assert rot == 24 and cos.shape == (300, 12) and cos.dtype == torch.float32
+    c, s = P.rope_angles(np.arange(300), P.rope_inv_freq(1e6, 24))
+    assert np.array_equal(cos.cpu().numpy(), c.astype(np.float32)) and np.array_equal(sin.cpu().numpy(), s.astype(np.float32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_swiglu_feed_forward_part(dtype):
+    from hk_b200.parts import SwiGLUFeedForward
+    part = SwiGLUFeedForward(72, 200, "mlp.")
+    prec, w = bind_random(part, dtype)
+    xb = (torch.randn(9, 72, device="cuda")).to(dtype)
+    res0 = torch.randn(9, 72, device="cuda")
+    res = res0.clone()
+    part.forward(xb, res, make_ctx(prec, [(0, 0, 9)]))
+    x = xb.double().cpu().numpy()
+    h = P.swiglu(P.linear(x, w["mlp.gate_proj.weight"]), P.linear(x, w["mlp.up_proj.weight"]))
+    want = res0.double().cpu().numpy() + P.linear(h, w["mlp.down_proj.weight"])
+    np.testing.assert_allclose(res.double().cpu().numpy(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("window,qk_norm,rope", [(None, True, True), (7, True, True), (None, False, False)])
+def test_attention_part_whole_then_cut(dtype, window, qk_norm, rope):
+    """The attention mixer alone: a whole sequence in one step equals the plain functions, and the
+    same sequence cut into a portion and single tokens gives the same rows."""
+    from hk_b200.cache.device import PagedCache
+    from hk_b200.parts import GQAAttention, RotaryEmbedding
+    d, H, G, hd, T = 40, 6, 2, 16, 29
+    pos_part = RotaryEmbedding(5000.0, 8, 64) if rope else None
+    part = GQAAttention(d, H, G, hd, "a.", qk_norm_eps=1e-5 if qk_norm else None, position=pos_part, window=window)
+    prec, w = bind_random(part, dtype, std=0.2)
+    xb = torch.randn(T, d, device="cuda").to(dtype)
+    x = xb.double().cpu().numpy()
+    q, k, v = (P.linear(x, w[f"a.{n}_proj.weight"]) for n in "qkv")
+    if qk_norm:
+        q, k = P.head_norm(q, w["a.q_norm.weight"], hd, 1e-5), P.head_norm(k, w["a.k_norm.weight"], hd, 1e-5)
+    if rope:
+        cos, sin = P.rope_angles(np.arange(T), P.rope_inv_freq(5000.0, 8))
+        q, k = P.rope_rotate_half(q, hd, cos, sin), P.rope_rotate_half(k, hd, cos, sin)
+    want = P.linear(P.causal_gqa_attention(q, k, v, H, G, hd, window=window), w["a.o_proj.weight"])
+
+    def run(cuts):
+        cache = PagedCache([part.cache_spec()], prec, 4, 16, 2, 64)
+        slot = cache.open()
+        other = cache.open()        # a second request shares the steps, so rows interleave
+        res = torch.zeros(T, d, device="cuda")
+        p = 0
+        for c in cuts:
+            r = torch.zeros(c + 1, d, device="cuda")
+            ctx = make_ctx(prec, [(other, int(cache.books.length[other]), 1), (slot, p, c)], cache)
+            part.forward(torch.cat([xb[:1], xb[p:p + c]]), r, ctx, cache.layers[0])
+            res[p:p + c] = r[1:]
+            p += c
+        return res.double().cpu().numpy()
+
+    whole = run([T])
+    np.testing.assert_allclose(whole, want, **tol(dtype))
+    cut = run([13, 2, 1, 1, 7, 5])
+    np.testing.assert_allclose(cut, want, **tol(dtype))
+    if dtype == torch.float32:
+        np.testing.assert_allclose(cut, whole, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_embedding_and_output_head_parts(dtype):
+    from hk_b200.parts import OutputHead, RMSNorm, TokenEmbedding
+    emb = TokenEmbedding(333, 72, "emb.weight")
+    prec, w = bind_random(emb, dtype)
+    ids = torch.tensor([5, 332, 0, 17], dtype=torch.int32, device="cuda")
+    x = torch.empty(4, 72, device="cuda")
+    emb.forward(ids, x)
+    assert np.array_equal(x.double().cpu().numpy(), w["emb.weight"][[5, 332, 0, 17]])
+    for tied in (False, True):
+        head = OutputHead(72, 333, RMSNorm(72, 1e-6, "norm.weight"), "head.weight", tied_to="emb.weight" if tied else None)
+        specs = head.param_specs()
+        assert specs["head.weight"].optional == tied
+        from hk_b200.weights import random_tensors
+        t = random_tensors(specs, 4, 0.05, 0.1, "cuda", dtype_of=lambda s: prec.working_dtype(s.kind))
+        if tied:
+            assert "head.weight" not in t
+            t["emb.weight"] = emb.table
+        head.bind(t, prec)
+        res = torch.randn(6, 72, device="cuda")
+        rows = torch.tensor([4, 1], dtype=torch.int32, device="cuda")
+        logits = head.forward(res, rows, 2, make_ctx(prec, [(0, 0, 6)]))
+        assert logits.dtype == torch.float32 and logits.shape == (2, 333)
+        wh = (t["emb.weight"] if tied else t["head.weight"]).double().cpu().numpy()
+        xb = P.rms_norm(res.double().cpu().numpy()[[4, 1]], t["norm.weight"].double().cpu().numpy(), 1e-6)
+        np.testing.assert_allclose(logits.double().cpu().numpy(), P.linear(xb, wh), **tol(dtype))
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy architecture defined here: a mixer whose memory is a state of fixed size (a decaying sum
+# of its inputs), beside an attention layer that is run twice and a layer that reads an earlier
+# layer's cache.  Nothing in the package knows about it.
+
+@dataclass
+class ToyConfig:
+    architecture: str = "ToyStateForCausalLM"
+    hidden_size: int = 24
+    vocab_size: int = 50
+    decay: float = 0.75
+    initializer_range: float = 0.2
+    max_position_embeddings: int = 64
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: v for k, v in raw.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(architectures=[self.architecture], hidden_size=self.hidden_size, vocab_size=self.vocab_size,
+                    decay=self.decay, initializer_range=self.initializer_range)
+
+
+def build_toy(cfg, max_positions):
+    from hk_b200.models import LayerCall, ModelSpec
+    from hk_b200.parts import (GQAAttention, MATRIX, OutputHead, ParamSpec, Part, PreNormBlock, RMSNorm, StateSpec,
+                               SwiGLUFeedForward, TokenEmbedding)
+
+    class DecayingSumMixer(Part):
+        """state <- decay * state + xb_t ; residual_t += W state   (state: one vector per request)"""
+
+        def __init__(self, d, decay, name):
+            self.d, self.decay, self.name, self.w = d, decay, name, None
+
+        def own_param_specs(self):
+            return {self.name: ParamSpec((self.d, self.d), MATRIX)}
+
+        def own_bind(self, tensors, precision):
+            self.w = tensors[self.name]
+
+        def cache_spec(self):
+            return StateSpec((self.d,), torch.float32)
+
+        def forward(self, xb, residual, ctx, cache, write_cache=True):
+            for slot, start, n in zip(ctx.slots, ctx.q_starts, ctx.q_lens):
+                st = cache.state[slot]
+                for t in range(start, start + n):
+                    st.mul_(self.decay).add_(xb[t].float())
+                    residual[t] += (self.w.float() @ st)
+
+    d = cfg.hidden_size
+    blocks = [
+        PreNormBlock(RMSNorm(d, 1e-6, "l0.n1"), DecayingSumMixer(d, cfg.decay, "l0.mix"), RMSNorm(d, 1e-6, "l0.n2"),
+                     SwiGLUFeedForward(d, 40, "l0.mlp.")),
+        PreNormBlock(RMSNorm(d, 1e-6, "l1.n1"), GQAAttention(d, 2, 1, 16, "l1.attn."), RMSNorm(d, 1e-6, "l1.n2"),
+                     SwiGLUFeedForward(d, 40, "l1.mlp.")),
+    ]
+    # layer 1 runs twice with a cache for each run, then once more reading the first run's cache
+    schedule = [LayerCall(0), LayerCall(1), LayerCall(1), LayerCall(1, cache_of=1)]
+    return ModelSpec(cfg, TokenEmbedding(cfg.vocab_size, d, "emb"), blocks,
+                     OutputHead(d, cfg.vocab_size, RMSNorm(d, 1e-6, "norm"), "head"), schedule)
+
+
+def toy_plain(cfg, w, ids):
+    """The toy model on whole sequences in float64, from the definitions above."""
+    d = cfg.hidden_size
+    x = w["emb"][ids]
+    T = len(ids)
+
+    def ffn(x, p):
+        xb = P.rms_norm(x, w[p + "n2"], 1e-6)
+        return x + P.linear(P.swiglu(P.linear(xb, w[p + "mlp.gate_proj.weight"]), P.linear(xb, w[p + "mlp.up_proj.weight"])),
+                            w[p + "mlp.down_proj.weight"])
+
+    xb = P.rms_norm(x, w["l0.n1"], 1e-6)
+    st = np.zeros(d)
+    add = np.zeros_like(x)
+    for t in range(T):
+        st = cfg.decay * st + xb[t]
+        add[t] = w["l0.mix"] @ st
+    x = ffn(x + add, "l0.")
+    first_kv = None
+    for call in range(3):
+        xb = P.rms_norm(x, w["l1.n1"], 1e-6)
+        q = P.linear(xb, w["l1.attn.q_proj.weight"])
+        k, v = P.linear(xb, w["l1.attn.k_proj.weight"]), P.linear(xb, w["l1.attn.v_proj.weight"])
+        if call == 0:
+            first_kv = (k, v)
+        if call == 2:
+            k, v = first_kv
+        x = x + P.linear(P.causal_gqa_attention(q, k, v, 2, 1, 16), w["l1.attn.o_proj.weight"])
+        x = ffn(x, "l1.")
+    return P.linear(P.rms_norm(x, w["norm"], 1e-6), w["head"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    from hk_b200.config import register_architecture
+    from hk_b200.engine import Engine, StepEntry
+    register_architecture("ToyStateForCausalLM", ToyConfig, build_toy)
+    cfg = ToyConfig()
+    eng = Engine(config=cfg, random_seed=3, dtype=dtype, max_tokens=128, page_tokens=4, max_requests=3, max_context=64)
+    kinds = [lc.kind for lc in eng.cache.layers]
+    assert kinds == ["state", "pages", "pages", "none"]
+    w = {}
+    blk0, blk1 = eng.model.layers
+    w.update({"emb": eng.model.embedding.table, "head": eng.model.head.weight, "norm": eng.model.head.norm.weight,
+              "l0.n1": blk0.mixer_norm.weight, "l0.n2": blk0.ffn_norm.weight, "l0.mix": blk0.mixer.w,
+              "l1.n1": blk1.mixer_norm.weight, "l1.n2": blk1.ffn_norm.weight})
+    for p, blk in (("l0.", blk0), ("l1.", blk1)):
+        F = blk.feed_forward.F
+        w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"] = blk.feed_forward.w_gate_up[:F], blk.feed_forward.w_gate_up[F:]
+        w[p + "mlp.down_proj.weight"] = blk.feed_forward.w_down
+    a = blk1.mixer
+    w["l1.attn.q_proj.weight"], w["l1.attn.k_proj.weight"], w["l1.attn.v_proj.weight"] = \
+        a.w_qkv[:32], a.w_qkv[32:48], a.w_qkv[48:]
+    w["l1.attn.o_proj.weight"] = a.w_o
+    w = {k: v.double().cpu().numpy() for k, v in w.items()}
+    rng = np.random.default_rng(0)
+    seqs = {"x": rng.integers(0, 50, 21).tolist(), "y": rng.integers(0, 50, 30).tolist()}
+    want = {k: toy_plain(cfg, w, np.array(v)) for k, v in seqs.items()}
+
+    def run(plan):
+        got = {k: [] for k in seqs}
+        fed = {k: 0 for k in seqs}
+        for k in seqs:
+            eng.open_request(k)
+        for step in plan:
+            entries = [StepEntry(k, seqs[k][fed[k]:fed[k] + n], list(range(n))) for k, n in step]
+            out = eng.step(entries).double().cpu().numpy()
+            r = 0
+            for k, n in step:
+                got[k].append(out[r:r + n])
+                r += n
+                fed[k] += n
+        for k in seqs:
+            eng.close_request(k)
+        return {k: np.concatenate(v) for k, v in got.items()}
+
+    whole = run([[("x", 21)], [("y", 30)]])
+    cut = run([[("x", 5), ("y", 2)], [("y", 11)], [("x", 1), ("y", 1)], [("x", 15), ("y", 16)]])
+    for k in seqs:
+        np.testing.assert_allclose(whole[k], want[k], **tol(dtype))
+        np.testing.assert_allclose(cut[k], want[k], **tol(dtype))
+    # the state slot was cleared when the requests were opened again: the second run equals the first
+    assert eng.free_pages() == [eng.cache.num_pages]
