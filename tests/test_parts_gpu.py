@@ -302,8 +302,11 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
 
     whole = run([[("x", 21)], [("y", 30)]])
     cut = run([[("x", 5), ("y", 2)], [("y", 11)], [("x", 1), ("y", 1)], [("x", 15), ("y", 16)]])
+    # the whole-model criterion of the replay tests: max |difference| relative to the largest |logit|
+    scale = max(np.abs(v).max() for v in want.values())
+    tol_max = 2e-5 if dtype == torch.float32 else 2e-2
     for k in seqs:
-        np.testing.assert_allclose(whole[k], want[k], **tol(dtype))
-        np.testing.assert_allclose(cut[k], want[k], **tol(dtype))
+        assert np.abs(whole[k] - want[k]).max() <= tol_max * scale
+        assert np.abs(cut[k] - want[k]).max() <= tol_max * scale
     # the state slot was cleared when the requests were opened again: the second run equals the first
     assert eng.free_pages() == [eng.cache.num_pages]
