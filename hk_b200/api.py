@@ -31,6 +31,11 @@ class GenerationStats:
     seconds: float = 0.0
     steps: int = 0
     preemptions: int = 0
+    decode_steps: int = 0          # steps after the last prompt portion: single tokens only
+    decode_tokens: int = 0
+    decode_seconds: float = 0.0
+    h2d_bytes_per_step: float = 0.0
+    d2h_bytes_per_step: float = 0.0
 
 
 def _as_prompts(prompts) -> (List[List[int]], bool):
@@ -63,10 +68,31 @@ def generate_with_engine(engine: Engine, prompts, max_new_tokens: int = 20, temp
                                 repeat_penalty=float(repeat_penalty), seed=0 if seed == 0 else seed + i)
         ids.append(sched.submit(p, max_new_tokens, params))
     t0 = time.perf_counter()
-    done = sched.run()
-    if stats is not None:
+    if stats is None:
+        done = sched.run()
+    else:
+        # time the tail of pure decode steps apart: it starts when the last prompt portion is in
+        t_dec, dec_steps, dec_tokens, h2d0, d2h0 = None, 0, 0, 0, 0
+        while sched.has_work():
+            prompt_before = sched.stats.prompt_tokens
+            dec_before = sched.stats.decode_tokens
+            sched.step()
+            if sched.stats.prompt_tokens != prompt_before or t_dec is None:
+                torch.cuda.synchronize()
+                t_dec, dec_steps, dec_tokens = time.perf_counter(), 0, 0
+                h2d0 = engine.stager.bytes + engine.cache.uploaded_bytes
+                d2h0 = sched.stats.d2h_bytes
+            else:
+                dec_steps += 1
+                dec_tokens += sched.stats.decode_tokens - dec_before
+        done = sched.finished
         torch.cuda.synchronize()
         stats.seconds = time.perf_counter() - t0
+        stats.decode_steps, stats.decode_tokens = dec_steps, dec_tokens
+        stats.decode_seconds = time.perf_counter() - (t_dec or t0)
+        if dec_steps:
+            stats.h2d_bytes_per_step = (engine.stager.bytes + engine.cache.uploaded_bytes - h2d0) / dec_steps
+            stats.d2h_bytes_per_step = (sched.stats.d2h_bytes - d2h0) / dec_steps
         stats.prompt_tokens = sched.stats.prompt_tokens
         stats.generated_tokens = sum(len(done[i].output) for i in ids)
         stats.steps = sched.stats.steps

@@ -52,6 +52,7 @@ class PagedCache:
         dev = precision.device
         self.tables = [torch.full((max_requests, self.books.max_pages_per_request), -1, dtype=torch.int32, device=dev)
                        for _ in keys]
+        self.uploaded_bytes = 0
         self.layers: List[LayerCache] = []
         self._states: List[torch.Tensor] = []
         for spec, gi in zip(cache_specs, entry_group):
@@ -90,6 +91,7 @@ class PagedCache:
         for slot in sorted(self.books.dirty):
             for g, dev_table in zip(self.books.groups, self.tables):
                 dev_table[slot].copy_(torch.from_numpy(g.table[slot].copy()))
+                self.uploaded_bytes += g.table.shape[1] * 4
         self.books.dirty.clear()
 
     def bytes(self) -> int:

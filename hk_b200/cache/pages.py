@@ -187,9 +187,9 @@ class CacheBooks:
         for g in self.groups:
             for i in range(int(g.n_pages[slot]), want_pages):
                 g.table[slot, i] = g.pool.take()
+                self.dirty.add(slot)
             g.n_pages[slot] = max(int(g.n_pages[slot]), want_pages)
         self.length[slot] = cur + n_new
-        self.dirty.add(slot)
 
     def truncate(self, slot: int, keep: int) -> None:
         """Rewinds `slot` to `keep` tokens, giving back the pages above (cf. src/engine/kv.zig:137-151).

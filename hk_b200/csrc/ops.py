@@ -52,12 +52,22 @@ def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) ->
         raise KernelError(f"{name} must be contiguous")
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launches this module has issued so far (for benchmarks' bookkeeping)."""
+    return _launches
+
+
+def _check(code: int, what: str, launches: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += launches
         return
     if code == _ERR_UNSUPPORTED:
         raise KernelError(f"{what}: the kernel refuses these sizes or types")
-    raise KernelError(f"{what}: CUDA error {code} ({torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+    raise KernelError(f"{what}: CUDA error {code}")
 
 
 # ---- kernel choice --------------------------------------------------------------------

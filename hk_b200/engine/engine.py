@@ -73,6 +73,39 @@ def _resolve_device(device) -> torch.device:
     return dev
 
 
+class PinnedStager:
+    """Host-to-device copies of a step's small integer arrays through pinned memory.
+
+    A ring of pinned buffers, each guarded by an event: a buffer is written again only after
+    the copy that last read it has finished, so the copies can be asynchronous."""
+
+    def __init__(self, device: torch.device, slots: int = 4):
+        self.device = device
+        self.slots = slots
+        self._bufs: List[Optional[torch.Tensor]] = [None] * slots
+        self._events: List[Optional[torch.cuda.Event]] = [None] * slots
+        self._next = 0
+        self.bytes = 0
+
+    def upload(self, arr: np.ndarray) -> torch.Tensor:
+        """A device int32 tensor with the contents (and shape) of `arr`."""
+        i = self._next
+        self._next = (i + 1) % self.slots
+        n = arr.size
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        if self._bufs[i] is None or self._bufs[i].numel() < n:
+            self._bufs[i] = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
+        host = self._bufs[i][:n]
+        host.numpy()[:] = arr.reshape(-1)
+        dev = host.to(self.device, non_blocking=True)
+        if self._events[i] is None:
+            self._events[i] = torch.cuda.Event()
+        self._events[i].record()
+        self.bytes += n * 4
+        return dev.view(arr.shape)
+
+
 class Engine:
     """A model bound to `cuda:device`, with a page pool for `max_tokens` cached tokens."""
 
@@ -111,6 +144,7 @@ class Engine:
         self._requests: Dict[Hashable, int] = {}
         self.plan_builder = None
         self.steps_run = 0
+        self.stager = PinnedStager(self.device)
 
     # -- requests ----------------------------------------------------------------------------
     def open_request(self, request: Hashable) -> None:
@@ -203,12 +237,12 @@ class Engine:
             q_starts.append(r)
             q_lens.append(m)
             r += m
-        meta_dev = torch.from_numpy(meta).to(self.device)
+        meta_dev = self.stager.upload(meta)
         ctx = StepContext(self.precision, n, meta_dev[0], meta_dev[1], meta_dev[2], slots, q_starts, q_lens,
                           starts, plan_builder=self.plan_builder)
         x = self.model.forward(ctx, self.cache.layers)
         self.steps_run += 1
         if not rows:
             return None
-        rows_dev = torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(self.device)
+        rows_dev = self.stager.upload(np.asarray(rows, dtype=np.int32))
         return self.model.head.forward(x, rows_dev, len(rows), ctx)

@@ -61,6 +61,7 @@ class SchedulerStats:
     decode_tokens: int = 0
     preemptions: int = 0
     finished: int = 0
+    d2h_bytes: int = 0
 
 
 class Scheduler:
@@ -226,6 +227,7 @@ class Scheduler:
         done: List[Request] = []
         if wanted:
             tokens = self.sampler.sample(logits, [r.sampling for r in wanted]).tolist()
+            self.stats.d2h_bytes += 4 * len(tokens)
             for r, tok in zip(wanted, tokens):
                 tok = int(tok)
                 self.sampler.accept(r.sampling, tok)
