@@ -178,27 +178,30 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
 }
 
 // ----------------------------------------------------------------------------- swiglu
-// out[t, j] = silu(gu[t, j]) * gu[t, F + j] for the fused projection gu[n, 2F] (gate | up).
+// out[t, j] = silu(gate_j) * up_j for the fused projection gu[n, 2F], laid out in blocks of
+// `block` gates followed by the matching `block` ups (block == F: all gates, then all ups).
 template <typename TO>
-__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   long long t = i / F;
   int j = (int)(i % F);
-  float g = gu[t * 2 * F + j];
-  float u = gu[t * 2 * F + F + j];
+  long long gi = t * 2 * F + (long long)(j / block) * 2 * block + (j % block);
+  float g = gu[gi];
+  float u = gu[gi + block];
   out[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
 }
 
-HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, void* stream) {
+HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, int block, void* stream) {
   if (n <= 0) return 0;
+  if (block <= 0 || F % block) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   long long total = (long long)n * F;
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (out_dtype == HK_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, (float*)out, total, F);
+    swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, (float*)out, total, F, block);
   else if (out_dtype == HK_BF16)
-    swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, (bf16*)out, total, F);
+    swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, (bf16*)out, total, F, block);
   else
     return HK_ERR_UNSUPPORTED;
   return hk_launch_status();

@@ -1,6 +1,119 @@
-"""Choice among the bfloat16 tensor-core matrix products (filled in as kernels land)."""
+"""Choice among the bfloat16 tensor-core matrix products.
+
+  * up to 64 rows (decode): the weight-streaming mma.sync kernel (`gemm_smallm.cu`);
+  * more rows (prefill, mixed batches): the persistent tcgen05 kernel (`gemm_tc.cu`).
+The choice depends on the shape alone.  Shapes both refuse (K not a multiple of 8, unaligned
+operands) go to the generic kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_UNSUPPORTED = 100001
+SMALL_M = 64
+_status = {}
+_sm_count = {}
 
 
-def run(a, w, out, accumulate, choice) -> bool:
-    """Runs a tensor-core kernel if one takes this shape; False sends the caller to the generic kernel."""
-    return False
+def status_flag(device: torch.device) -> torch.Tensor:
+    """Device int32 that a timed-out wait inside a tensor-core kernel sets to 1."""
+    key = device.index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device: torch.device) -> None:
+    """Raises if a kernel recorded a timed-out wait (synchronises with the device)."""
+    key = device.index or 0
+    if key in _status and int(_status[key].item()) != 0:
+        _status[key].zero_()
+        raise RuntimeError("a tensor-core kernel gave up waiting on a barrier; its results are invalid")
+
+
+def _sms(device: torch.device) -> int:
+    key = device.index or 0
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_count[key]
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _aligned(a, w) -> bool:
+    return a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def row_tiles(M: int, N: int, device) -> int:
+    """Row tiles of 16 per CTA for the small-M kernel: as fat as the grid allows while it still
+    fills the SMs twice over (fat CTAs read the activations from L2 less often)."""
+    sms = _sms(device)
+    limit = 4 if M <= 16 else 2
+    rt = limit
+    while rt > 1 and -(-N // (16 * rt)) < 2 * sms:
+        rt //= 2
+    return rt
+
+
+def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
+    """out (fp32) = a w^T (+ out).  Returns False when no tensor-core kernel takes the shape."""
+    from . import ops
+    M, K = a.shape
+    N = w.shape[0]
+    if not _aligned(a, w):
+        return False
+    if choice == "smallm" or (choice is None and M <= SMALL_M):
+        if M > SMALL_M:
+            return False
+        lib = build.load("gemm_smallm")
+        code = lib.hk_gemm_smallm(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(N), 1 if accumulate else 0,
+                                  row_tiles(M, N, a.device), _stream())
+        if code == _UNSUPPORTED:
+            return False
+        ops._check(code, "gemm (small-M)")
+        return True
+    lib = build.load("gemm_tc")
+    bn = 256 if N >= 256 and -(-M // 128) * -(-N // 256) >= _sms(a.device) // 2 else 128
+    code = lib.hk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(N), 1 if accumulate else 0, bn,
+                          _ptr(status_flag(a.device)), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    ops._check(code, "gemm (tcgen05)")
+    return True
+
+
+def run_swiglu(a, w_paired, out) -> bool:
+    """out (bf16 [M, F]) = silu(gate) * up of a w^T, for a weight laid out [128 gate | 128 up] per
+    256 rows (see `pair_gate_up`).  tcgen05 kernel only; False when it refuses."""
+    from . import ops
+    M, K = a.shape
+    N = w_paired.shape[0]
+    if not _aligned(a, w_paired) or N % 256 or out.shape[1] % 8:
+        return False
+    lib = build.load("gemm_tc")
+    code = lib.hk_gemm_tc(_ptr(a), _ptr(w_paired), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2, 256,
+                          _ptr(status_flag(a.device)), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    ops._check(code, "gemm+swiglu (tcgen05)")
+    return True
+
+
+PAIR = 128
+
+
+def pair_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[F, d] gate and up -> [2F, d] with rows [128 gate | 128 up | 128 gate | ...]; F % 128 == 0."""
+    F, d = gate.shape
+    return torch.stack([gate.view(F // PAIR, PAIR, d), up.view(F // PAIR, PAIR, d)], dim=1).reshape(2 * F, d).contiguous()

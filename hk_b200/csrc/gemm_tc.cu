@@ -1,0 +1,382 @@
+// bf16 matrix product on the 5th-generation tensor cores: out[M, N] = a[M, K] * w[N, K]^T with fp32
+// accumulation in tensor memory.  One persistent CTA per SM walks over 128 x BN output tiles.
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the a tile [128 x 64] and the w tile
+//               [BN x 64] (128-byte swizzle) into a ring of shared-memory stages
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x BN x 16, both operands
+//               K-major from shared memory) and commits stage releases / accumulator-ready signals
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one row per thread), then one of
+//               STORE (fp32), ADD (fp32 += : the residual sum), SWIGLU (bf16 silu(gate)*up from a
+//               weight whose rows are laid out [128 gate | 128 up] per tile)
+// Two accumulator buffers (2 x BN columns of tensor memory) let the epilogue of one tile overlap
+// the main loop of the next.  Every mbarrier wait is bounded: on time-out the CTA records an
+// error in `status`, all roles leave their loops, tensor memory is freed and the kernel returns.
+// No cluster multicast is used anywhere: every CTA loads its own tiles.
+//
+// Reference counterpart: `gemm_tc_<fmt>` (mma.sync, 64 x 128 blocks), src/cuda_device.zig:348-499.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one timed out).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes with the 128-byte swizzle: 8-row groups are
+// 1024 bytes apart (stride byte offset); the leading byte offset is unused (1); version 1 = sm_100.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN, int STAGES>
+struct SharedStorage {
+  alignas(1024) uint8_t a[STAGES][BM * BK * 2];
+  alignas(1024) uint8_t b[STAGES][BN * BK * 2];
+  alignas(8) uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+               int M, int N, int K, long long ldo, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  using Storage = SharedStorage<BN, STAGES>;
+  Storage& sm = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  volatile int* abort_flag = &sm.abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN;   // 256 or 512: a power of two >= 32
+  constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.tmem_full[b], 1);
+      mbar_init(&sm.tmem_empty[b], 4);
+    }
+    sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sm.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&sm.full[stage], STAGE_BYTES);
+          tma_load_2d(sm.a[stage], &map_a, &sm.full[stage], kb * BK, m0);
+          tma_load_2d(sm.b[stage], &map_w, &sm.full[stage], kb * BK, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N and M encoded
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = (uint32_t)(local >> 1);
+        if (!mbar_wait(&sm.tmem_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sm.full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_u32(sm.a[stage]));
+          const uint64_t db = make_smem_desc(smem_u32(sm.b[stage]));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advance both start addresses by 32 bytes (16 bf16) inside the swizzled row
+            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(&sm.empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&sm.tmem_full[buf]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;                     // the TMEM lanes this warp may read: 32*quarter ..
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t use = (uint32_t)(local >> 1);
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+      if (!mbar_wait(&sm.tmem_full[buf], use & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      if (EPI == EPI_SWIGLU) {
+        // columns [0, BN/2) are gates, [BN/2, BN) the matching ups; output columns (n0 / 2) + c
+        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + (n0 >> 1);
+        const int n_out = (N >> 1) - (n0 >> 1);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + (uint32_t)c0, g);
+          tmem_ld32(taddr + (uint32_t)(BN / 2 + c0), u);
+          tmem_ld_wait();
+          if (row < M) {
+            if (c0 + 32 <= n_out && (ldo & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
+                  float h0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[j + 2 * e]);
+                  float h1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
+                  __nv_bfloat162 p = __floats2bfloat162_rn(h0, h1);
+                  packed[e] = *reinterpret_cast<uint32_t*>(&p);
+                }
+                *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < n_out) {
+                  float gv = __uint_as_float(g[j]);
+                  o[c0 + j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * __uint_as_float(u[j]));
+                }
+            }
+          }
+        }
+      } else {
+        float* o = reinterpret_cast<float*>(out) + (size_t)row * ldo + n0;
+        const int n_out = N - n0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + (uint32_t)c0, v);
+          tmem_ld_wait();
+          if (row < M) {
+            if (c0 + 32 <= n_out && (ldo & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 x = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                       __uint_as_float(v[j + 3]));
+                float4* p = reinterpret_cast<float4*>(o + c0 + j);
+                if (EPI == EPI_ADD) {
+                  float4 y = *p;
+                  x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                }
+                *p = x;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < n_out) {
+                  float x = __uint_as_float(v[j]);
+                  o[c0 + j] = EPI == EPI_ADD ? o[c0 + j] + x : x;
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.tmem_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && sm.abort_flag) atomicExch(status, 1);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side: tensor maps ------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// bf16 matrix [rows, cols] with `cols` contiguous; box = 64 columns x box_rows rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, int STAGES, int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int* status, cudaStream_t s) {
+  static bool configured = false;
+  const size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_tc_kernel<BN, STAGES, EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, status);
+  return hk_launch_status();
+}
+
+}  // namespace
+
+// out = a w^T.  epilogue 0: out fp32 [M, N] stored; 1: out fp32 [M, N] += ; 2: out bf16 [M, N/2] =
+// silu(gate) * up with w's rows laid out [128 gate | 128 up] per 256-row tile.  `status` is a device int
+// that a timed-out wait sets to 1 (the caller reads it when it next synchronises).
+// Requirements (else HK_ERR_UNSUPPORTED): K % 8 == 0, a and w 16-byte aligned, for epilogue 2 N % 256 == 0.
+HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
+                      int* status, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU && ((N & 255) || bn != 256)) return HK_ERR_UNSUPPORTED;
+  if (bn != 128 && bn != 256) return HK_ERR_UNSUPPORTED;
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, N, K, bn)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bn == 256) {
+    if (epilogue == EPI_STORE) return launch<256, 4, EPI_STORE>(ma, mw, out, M, N, K, ldo, status, s);
+    if (epilogue == EPI_ADD) return launch<256, 4, EPI_ADD>(ma, mw, out, M, N, K, ldo, status, s);
+    if (epilogue == EPI_SWIGLU) return launch<256, 4, EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, status, s);
+  } else {
+    if (epilogue == EPI_STORE) return launch<128, 6, EPI_STORE>(ma, mw, out, M, N, K, ldo, status, s);
+    if (epilogue == EPI_ADD) return launch<128, 6, EPI_ADD>(ma, mw, out, M, N, K, ldo, status, s);
+  }
+  return HK_ERR_UNSUPPORTED;
+}

@@ -134,15 +134,36 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
 # ---- swiglu ---------------------------------------------------------------------------
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, F + j]  (gate_up float32 [n, 2F])."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[t, j] = silu(gate) * up for gate_up float32 [n, 2F].  With block = 0 the row is laid out
+    [F gates | F ups]; with block = b (dividing F) it is [b gates | b ups | b gates | ...]."""
     _need(gate_up, "gate_up", torch.float32, 2)
     _need(out, "out", dims=2)
     n, f = out.shape
-    if gate_up.shape[0] != n or gate_up.shape[1] != 2 * f:
-        raise KernelError("swiglu: gate_up must be [n, 2F] for out [n, F]")
+    block = block or f
+    if gate_up.shape[0] != n or gate_up.shape[1] != 2 * f or f % block:
+        raise KernelError("swiglu: gate_up must be [n, 2F] for out [n, F], and the block must divide F")
     lib = build.load("elementwise")
-    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, _stream()), "swiglu")
+    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), _stream()), "swiglu")
+
+
+def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, block: int) -> None:
+    """out[M, F] = silu(gate) * up of a @ w_paired^T, w_paired [2F, K] laid out [block gates | block ups |
+    ...] (block = 0: [F gates | F ups]).  Fused into the tensor-core product's epilogue when that takes the
+    shape, else a product to float32 followed by the swiglu kernel."""
+    _need(a, "a", dims=2)
+    _need(w_paired, "w", a.dtype, 2)
+    _need(out, "out", a.dtype, 2)
+    M, F = out.shape
+    if a.shape[0] != M or w_paired.shape != (2 * F, a.shape[1]):
+        raise KernelError("gemm_swiglu: shapes do not fit")
+    if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc") and M > 64:
+        from . import gemm_fast
+        if block == gemm_fast.PAIR and gemm_fast.run_swiglu(a, w_paired, out):
+            return
+    gu = torch.empty((M, 2 * F), dtype=torch.float32, device=a.device)
+    gemm(a, w_paired, gu)
+    swiglu(gu, out, block)
 
 
 # ---- per-head norm + rotation + cache write ---------------------------------------------

@@ -16,6 +16,7 @@ class SwiGLUFeedForward(Part):
     def __init__(self, hidden: int, intermediate: int, prefix: str):
         self.hidden, self.F, self.prefix = hidden, intermediate, prefix
         self.w_gate_up = self.w_down = None
+        self.block = 0
 
     def own_param_specs(self) -> Dict[str, ParamSpec]:
         p = self.prefix
@@ -27,15 +28,22 @@ class SwiGLUFeedForward(Part):
 
     def own_bind(self, tensors, precision: Precision) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], dim=0).contiguous()
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        # Serving layout: rows in blocks of 128 gates followed by their 128 ups, so that one output tile
+        # of the tensor-core product holds both halves and SwiGLU runs in its epilogue
+        # (cf. the interleaved gate/up of shaders/swiglu_pair.comp:2).  Otherwise [all gates | all ups].
+        from ..csrc import gemm_fast
+        if precision.compute == torch.bfloat16 and self.F % gemm_fast.PAIR == 0:
+            self.block = gemm_fast.PAIR
+            self.w_gate_up = gemm_fast.pair_gate_up(gate, up)
+        else:
+            self.block = 0
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"]
 
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx) -> None:
-        n = xb.shape[0]
-        gate_up = torch.empty((n, 2 * self.F), dtype=torch.float32, device=xb.device)
-        ops.gemm(xb, self.w_gate_up, gate_up)
-        h = torch.empty((n, self.F), dtype=xb.dtype, device=xb.device)
-        ops.swiglu(gate_up, h)
+        h = torch.empty((xb.shape[0], self.F), dtype=xb.dtype, device=xb.device)
+        ops.gemm_swiglu(xb, self.w_gate_up, h, self.block)
         ops.gemm(h, self.w_down, residual, accumulate=True)
 
 

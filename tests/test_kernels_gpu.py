@@ -251,3 +251,84 @@ def test_kernels_refuse_what_they_cannot_do():
         z = torch.zeros(1, dtype=torch.int32, device=DEV)
         o.paged_attention(torch.zeros(1, 272, device=DEV), torch.zeros(1, 1, 4, 272, device=DEV), torch.zeros(1, 1, 4, 272, device=DEV),
                           torch.zeros(1, 1, dtype=torch.int32, device=DEV), z, z, torch.zeros(1, 272, device=DEV), 1, 1, 272, 4, 0, 1.0)
+
+
+# ---- the tensor-core matrix products (bfloat16) ---------------------------------------------------
+
+
+def gemm_case(kernel, m, n, k, accumulate, seed=0):
+    g = torch.Generator().manual_seed(seed + m * 7 + n * 3 + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    out0 = torch.randn(m, n, generator=g)
+    out = out0.clone().to(DEV)
+    with ops().force(gemm=kernel):
+        ops().gemm(a.to(DEV), w.to(DEV), out, accumulate=accumulate)
+    from hk_b200.csrc import gemm_fast
+    gemm_fast.check_status(torch.device(DEV))
+    want = ref_ops.gemm(a, w, out0 if accumulate else None)
+    bound = a.double().abs() @ w.double().abs().T
+    err = (out.double().cpu() - want).abs()
+    ok = err <= 2e-6 * bound + 1e-6 * want.abs() + 1e-6
+    assert ok.all(), f"{int((~ok).sum())} of {ok.numel()} wrong; worst {err.max():.3g} at {tuple(np.unravel_index(int(err.argmax()), err.shape))}"
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 256, 64), (128, 128, 64), (256, 512, 128), (130, 300, 72), (65, 1000, 4096), (2048, 6144, 512), (300, 151936 // 8, 256),
+    (128, 256, 8), (1000, 136, 1024), (129, 257, 200)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_tcgen05(m, n, k, accumulate):
+    gemm_case("tc", m, n, k, accumulate)
+
+
+def test_gemm_tcgen05_many_tiles_per_cta():
+    # more tiles than SMs x 2: every CTA walks several tiles through both accumulator buffers
+    gemm_case("tc", 2048, 24576, 256, False)
+    gemm_case("tc", 4096, 4096, 4096, True)
+
+
+@pytest.mark.parametrize("m", [1, 2, 7, 8, 9, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k", [(16, 64), (300, 72), (1000, 4096), (4096, 12288), (6144, 512), (40, 8), (18992, 128)])
+def test_gemm_small_m(m, n, k):
+    gemm_case("smallm", m, n, k, False)
+    gemm_case("smallm", m, n, k, True, seed=1)
+
+
+def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
+    a = torch.randn(4, 70).to(torch.bfloat16).to(DEV)      # K % 8 != 0
+    w = torch.randn(9, 70).to(torch.bfloat16).to(DEV)
+    out = torch.empty(4, 9, device=DEV)
+    for kernel in ("tc", "smallm"):
+        with pytest.raises(ops().KernelError):
+            with ops().force(gemm=kernel):
+                ops().gemm(a, w, out)
+    ops().gemm(a, w, out)                                  # free choice: falls to the generic kernel
+    close(out, ref_ops.gemm(a.cpu(), w.cpu()), torch.float32, atol=1e-4, rtol=1e-4)
+    with pytest.raises(ops().KernelError):
+        with ops().force(gemm="smallm"):
+            ops().gemm(torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV),
+                       torch.zeros(65, 8, device=DEV))
+
+
+@pytest.mark.parametrize("m,f,k", [(128, 128, 64), (300, 384, 200), (2048, 1536, 512), (7, 256, 128), (64, 128, 64), (65, 128, 64)])
+def test_gemm_swiglu_paired_layout(m, f, k):
+    from hk_b200.csrc import gemm_fast
+    g = torch.Generator().manual_seed(m + f + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    up = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    paired = gemm_fast.pair_gate_up(gate, up)
+    assert torch.equal(paired[:128], gate[:128]) and torch.equal(paired[128:256], up[:128])
+    out = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_swiglu(a.to(DEV), paired.to(DEV), out, gemm_fast.PAIR)
+    gemm_fast.check_status(torch.device(DEV))
+    want = ref_ops.swiglu(torch.cat([ref_ops.gemm(a, gate), ref_ops.gemm(a, up)], dim=1))
+    close(out, want, torch.bfloat16, atol=2e-3)
+    # the unfused route over the same layout, and the plain [gates | ups] layout
+    with ops().force(gemm="generic"):
+        out2 = torch.empty_like(out)
+        ops().gemm_swiglu(a.to(DEV), paired.to(DEV), out2, gemm_fast.PAIR)
+        out3 = torch.empty_like(out)
+        ops().gemm_swiglu(a.to(DEV), torch.cat([gate, up]).to(DEV), out3, 0)
+    close(out2, want, torch.bfloat16, atol=2e-3)
+    close(out3, want, torch.bfloat16, atol=2e-3)
