@@ -1,5 +1,125 @@
-"""Choice of the bfloat16 flash attention kernel (filled in as the kernel lands)."""
+"""Plan and launch of the bfloat16 flash attention kernel (`attention_flash.cu`).
+
+A *plan* cuts one step's batch into the kernel's work items for a given (window, heads,
+groups): each item is a run of consecutive query tokens of one request and a range of keys.
+Runs hold as many tokens as fit the CTA's rows (16 per warp, one row per (token, head of the
+group)).  When the batch alone would leave SMs idle (decode: few requests, long contexts),
+a run's keys are split among several items; their partial results are merged by the combine
+kernel.  The plan depends only on the batch's shape (who has how many tokens at which
+positions), never on values.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import numpy as np
+import torch
+
+from . import build
+
+_UNSUPPORTED = 100001
+TILE_N = 64
+MAX_HD = 128
 
 
-def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan) -> bool:
-    return False
+@dataclass
+class FlashPlan:
+    nw: int                      # warps per CTA
+    n_items: int
+    items: torch.Tensor          # int32 [n_items, 8] on the device
+    n_parts: int                 # partial results in scratch (0: none)
+    first: Optional[torch.Tensor] = None   # per token: first partial, number of partials, row within the item
+    count: Optional[torch.Tensor] = None
+    row0: Optional[torch.Tensor] = None
+
+
+def supported(hd: int, group: int) -> bool:
+    return hd % 16 == 0 and 16 <= hd <= MAX_HD and group <= 64
+
+
+def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
+               sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0) -> Optional[FlashPlan]:
+    """`upload(int32 array) -> device tensor`.  `fixed_splits` > 0 forces that many items per run
+    (a shape that does not change from step to step, for captured decode graphs)."""
+    group = H // G
+    nw = 1 if all(l == 1 for l in q_lens) else 4
+    rows = 16 * nw
+    if group > rows:
+        if group > 64:
+            return None
+        nw, rows = 4, 64
+    tpb = rows // group
+    runs = []
+    for slot, qs, ql, p0 in zip(slots, q_starts, q_lens, start_positions):
+        for b0 in range(0, ql, tpb):
+            n = min(tpb, ql - b0)
+            pos0 = p0 + b0
+            kv_hi = pos0 + n
+            kv_lo = max(0, pos0 - window + 1) if window > 0 else 0
+            runs.append((qs + b0, n, slot, pos0, kv_lo, kv_hi))
+    base_ctas = len(runs) * G
+    items = np.zeros((0, 8), dtype=np.int32)
+    recs = []
+    first = np.zeros(n_tokens, dtype=np.int32)
+    count = np.zeros(n_tokens, dtype=np.int32)
+    row0 = np.zeros(n_tokens, dtype=np.int32)
+    n_parts = 0
+    for (q_row0, n, slot, pos0, kv_lo, kv_hi) in runs:
+        kv_len = kv_hi - kv_lo
+        if fixed_splits > 0:
+            want = fixed_splits
+        elif base_ctas >= 2 * sm_count:
+            want = 1
+        else:
+            want = max(1, min(-(-2 * sm_count // base_ctas), kv_len // 128))
+        chunk = -(-(-(-kv_len // want)) // TILE_N) * TILE_N
+        n_split = fixed_splits if fixed_splits > 0 else max(1, -(-kv_len // chunk))
+        if n_split == 1:
+            recs.append((q_row0, n, slot, pos0, kv_lo, kv_hi, -1, 0))
+            continue
+        # splits start on tile boundaries of absolute key positions, so a tile is never shared
+        start = (kv_lo // TILE_N) * TILE_N
+        for s in range(n_split):
+            a = max(kv_lo, start + s * chunk)
+            b = min(kv_hi, start + (s + 1) * chunk)
+            recs.append((q_row0, n, slot, pos0, a, max(a, b), n_parts + s, 0))
+        for tq in range(n):
+            first[q_row0 + tq], count[q_row0 + tq], row0[q_row0 + tq] = n_parts, n_split, tq * group
+        n_parts += n_split
+    items = np.asarray(recs, dtype=np.int32).reshape(-1, 8)
+    plan = FlashPlan(nw, len(recs), upload(items), n_parts)
+    if n_parts:
+        meta = upload(np.stack([first, count, row0]))
+        plan.first, plan.count, plan.row0 = meta[0], meta[1], meta[2]
+    return plan
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan: FlashPlan) -> bool:
+    from . import ops
+    if not supported(hd, H // G) or plan is None:
+        return False
+    lib = build.load("attention_flash")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rows = 16 * plan.nw
+    part_o = part_ml = None
+    if plan.n_parts:
+        part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
+    code = lib.hk_attention_flash(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]),
+                                  _ptr(plan.items), plan.n_items, plan.nw, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
+                                  int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), stream)
+    if code == _UNSUPPORTED:
+        return False
+    ops._check(code, "paged_attention (flash)")
+    if plan.n_parts:
+        code = lib.hk_attention_combine(_ptr(part_o), _ptr(part_ml), _ptr(plan.first), _ptr(plan.count), _ptr(plan.row0),
+                                        _ptr(out), q.shape[0], H, G, hd, rows, stream)
+        ops._check(code, "paged_attention (combine)")
+    return True

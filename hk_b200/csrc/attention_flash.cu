@@ -1,0 +1,350 @@
+// Flash attention over the paged cache for bf16 serving: prompt portions, decode tokens and mixed
+// batches in one kernel, grouped-query aware, with optional key splitting for long contexts.
+//
+// Work is cut on the host into *items*: (request slot, a run of consecutive query tokens, a key range).
+// A CTA takes one item for one kv head.  Its rows are (query token, query head of the group) pairs, 16 per
+// warp, so the K/V pages of a kv head are read once for all the heads that share it.  Keys come in tiles of
+// 64 through cp.async (double buffered) from wherever the block table says the pages are; scores and
+// weighted values run on mma.sync.m16n8k16 (bf16 in, fp32 out) with the softmax state (max, sum) in fp32
+// registers, as in the reference's single-sequence kernel `attention_tc_128`
+// (src/cuda_device.zig:1069-1248), which this replaces together with its split-KV decode kernels
+// `attention_part_warp` + `attention_combine` (:1654-1815).  A row at position p sees keys
+// [max(0, p - window + 1), p]; its own key was written earlier in the step.
+//
+// With splitting, each CTA writes an unnormalised partial (values, max, sum) to scratch and
+// `attention_combine_kernel` merges the partials of a (token, head) exactly, in split order.
+// Head sizes: multiples of 16 up to 128.  Any group size up to 16 * warps.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_N = 64;
+
+struct Item {
+  int q_row0;     // row of the first query token in the batch
+  int n_tokens;   // query tokens of this item
+  int slot;       // request slot (row of the block table)
+  int pos0;       // position of the first query token
+  int kv_lo;      // first key this item may read
+  int kv_hi;      // one past the last key
+  int part;       // index of the partial in scratch, or -1: write the output directly
+  int pad;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, int NW>
+__global__ void __launch_bounds__(NW * 32)
+attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                       const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
+                       bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
+                       int page_tokens, int window, float scale_log2) {
+  constexpr int ROWS = NW * 16;
+  constexpr int LD = HD + 8;            // padded row: (HD/8 + 1) 16-byte chunks, an odd count -> no ldmatrix conflicts
+  constexpr int CPR = HD / 8;           // 16-byte chunks per row
+  constexpr int KSTEPS = HD / 16;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* ks = reinterpret_cast<bf16*>(smem_raw);             // [2][TILE_N][LD]
+  bf16* vs = ks + 2 * TILE_N * LD;                          // [2][TILE_N][LD]
+
+  const Item it = items[blockIdx.x];
+  const int g = blockIdx.y;
+  const int group = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qr = lane >> 2, qt = lane & 3;
+  const int* bt = block_table + (size_t)it.slot * table_stride;
+
+  // the two rows this thread owns in its warp's 16: r0 and r0 + 8
+  int row[2], pos[2], lo[2];
+  bool valid[2];
+  const bf16* qp[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    row[i] = warp * 16 + qr + 8 * i;
+    int tq = row[i] / group;
+    valid[i] = tq < it.n_tokens;
+    if (!valid[i]) tq = 0;
+    pos[i] = it.pos0 + tq;
+    lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;
+    qp[i] = q + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
+  }
+
+  // Q fragments (A operand): per k-step a0 = (r0, d 2t..), a1 = (r0+8, d 2t..), a2 = (r0, d 2t+8..), a3 = (r0+8, d 2t+8..)
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int s = 0; s < KSTEPS; ++s) {
+    qf[s][0] = *reinterpret_cast<const uint32_t*>(qp[0] + s * 16 + 2 * qt);
+    qf[s][1] = *reinterpret_cast<const uint32_t*>(qp[1] + s * 16 + 2 * qt);
+    qf[s][2] = *reinterpret_cast<const uint32_t*>(qp[0] + s * 16 + 8 + 2 * qt);
+    qf[s][3] = *reinterpret_cast<const uint32_t*>(qp[1] + s * 16 + 8 + 2 * qt);
+  }
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+
+  const int t_begin = it.kv_lo / TILE_N;
+  const int t_end = (it.kv_hi + TILE_N - 1) / TILE_N;
+
+  auto load_tile = [&](int t, int stage) {
+    bf16* kd = ks + stage * TILE_N * LD;
+    bf16* vd = vs + stage * TILE_N * LD;
+    for (int idx = threadIdx.x; idx < TILE_N * CPR; idx += NW * 32) {
+      const int r = idx / CPR, c = idx % CPR;
+      const int j = t * TILE_N + r;
+      const bool ok = j >= it.kv_lo && j < it.kv_hi;
+      size_t off = 0;
+      if (ok) {
+        const int page = bt[j / page_tokens];
+        off = (((size_t)max(page, 0) * G + g) * page_tokens + (j % page_tokens)) * HD + c * 8;
+      }
+      cp_async16(kd + r * LD + c * 8, k_pages + off, ok);
+      cp_async16(vd + r * LD + c * 8, v_pages + off, ok);
+    }
+  };
+
+  if (t_begin < t_end) load_tile(t_begin, 0);
+  cp_async_commit();
+  for (int t = t_begin; t < t_end; ++t) {
+    const int stage = (t - t_begin) & 1;
+    if (t + 1 < t_end) load_tile(t + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* kt = ks + stage * TILE_N * LD;
+    const bf16* vt = vs + stage * TILE_N * LD;
+
+    // ---- scores: 16 rows x 64 keys per warp
+    float s[TILE_N / 8][4];
+#pragma unroll
+    for (int n = 0; n < TILE_N / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+      for (int np = 0; np < TILE_N / 16; ++np) {
+        uint32_t b[4];
+        const int mi = lane >> 3, r8 = lane & 7;
+        ldmatrix_x4(b, kt + (np * 16 + (mi >> 1) * 8 + r8) * LD + kk * 16 + (mi & 1) * 8);
+        mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    // ---- mask, scale, running maximum
+    float mt[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+    for (int n = 0; n < TILE_N / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int j = t * TILE_N + n * 8 + 2 * qt + (e & 1);
+        const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
+        s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
+        mt[i] = fmaxf(mt[i], s[n][e]);
+      }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mt[i] = fmaxf(mt[i], __shfl_xor_sync(0xffffffffu, mt[i], 1));
+      mt[i] = fmaxf(mt[i], __shfl_xor_sync(0xffffffffu, mt[i], 2));
+      const float mn = fmaxf(m[i], mt[i]);
+      msafe[i] = mn == -CUDART_INF_F ? 0.f : mn;
+      corr[i] = exp2f(m[i] - msafe[i]);       // m = -inf -> 0
+      m[i] = mn;
+      l[i] *= corr[i];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+      o[n][0] *= corr[0];
+      o[n][1] *= corr[0];
+      o[n][2] *= corr[1];
+      o[n][3] *= corr[1];
+    }
+    // ---- probabilities (bf16 A fragments) and weighted values
+#pragma unroll
+    for (int kk = 0; kk < TILE_N / 16; ++kk) {
+      uint32_t pf[4];
+      float p[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[h][e] = exp2f(s[2 * kk + h][e] - msafe[e >> 1]);
+          l[e >> 1] += p[h][e];
+        }
+      pf[0] = pack_bf16(p[0][0], p[0][1]);
+      pf[1] = pack_bf16(p[0][2], p[0][3]);
+      pf[2] = pack_bf16(p[1][0], p[1][1]);
+      pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t b[4];
+        const int mi = lane >> 3, r8 = lane & 7;
+        ldmatrix_x4_trans(b, vt + (kk * 16 + (mi & 1) * 8 + r8) * LD + dp * 16 + (mi >> 1) * 8);
+        mma_bf16(o[2 * dp], pf, b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+      }
+    }
+    __syncthreads();   // the stage is free for the load after next
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  if (it.part < 0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (!valid[i]) continue;
+      const int tq = row[i] / group;
+      bf16* op = out + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
+      const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<uint32_t*>(op + n * 8 + 2 * qt) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+  } else {
+    const size_t base = ((size_t)it.part * G + g) * ROWS;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float* po = part_o + (base + row[i]) * HD;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<float2*>(po + n * 8 + 2 * qt) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+      if (qt == 0) *reinterpret_cast<float2*>(part_ml + (base + row[i]) * 2) = make_float2(m[i], l[i]);
+    }
+  }
+}
+
+// One warp per (token, head): merges `count[t]` partials starting at `first[t]` (row `row0[t] + head % group`).
+// Tokens with count 0 were written directly by the main kernel.
+template <int HD>
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const int* __restrict__ first, const int* __restrict__ count,
+                                         const int* __restrict__ row0, bf16* __restrict__ out, int n_tokens, int H, int G,
+                                         int rows) {
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= n_tokens * H) return;
+  const int t = w / H, h = w % H;
+  const int n = count[t];
+  if (n <= 0) return;
+  const int group = H / G, g = h / group;
+  const int r = row0[t] + h % group;
+  float mm = -CUDART_INF_F;
+  for (int s = 0; s < n; ++s) mm = fmaxf(mm, part_ml[(((size_t)(first[t] + s) * G + g) * rows + r) * 2]);
+  float acc[(HD + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+  float lsum = 0.f;
+  for (int s = 0; s < n; ++s) {
+    const size_t base = ((size_t)(first[t] + s) * G + g) * rows + r;
+    const float ms = part_ml[base * 2], ls = part_ml[base * 2 + 1];
+    const float f = ms == -CUDART_INF_F ? 0.f : exp2f(ms - mm);
+    lsum += ls * f;
+#pragma unroll
+    for (int i = 0; i < (HD + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < HD) acc[i] += part_o[base * HD + d] * f;
+    }
+  }
+  const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+  bf16* op = out + ((size_t)t * H + h) * HD;
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < HD) op[d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+template <int HD, int NW>
+int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
+                 void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, cudaStream_t s) {
+  const size_t smem = (size_t)4 * TILE_N * (HD + 8) * sizeof(bf16);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((unsigned)n_items, (unsigned)G);
+  attention_flash_kernel<HD, NW><<<grid, NW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
+                                                            (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
+                                                            scale_log2);
+  return hk_launch_status();
+}
+
+template <int HD>
+int launch_hd(int nw, const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
+              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, cudaStream_t s) {
+  if (nw == 1) return launch_flash<HD, 1>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, s);
+  if (nw == 4) return launch_flash<HD, 4>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, s);
+  return HK_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+// items: device array of n_items records of 8 ints (see `Item`).  nw: warps per CTA (1 or 4); an item holds at
+// most (16 * nw) / (H / G) query tokens.  part_o [parts, G, 16*nw, hd] and part_ml [parts, G, 16*nw, 2] are
+// fp32 scratch for items with part >= 0.  scale_log2 = scale * log2(e).
+HK_API int hk_attention_flash(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                              int table_stride, const void* items, int n_items, int nw, void* out, float* part_o,
+                              float* part_ml, int H, int G, int hd, int page_tokens, int window, float scale_log2,
+                              void* stream) {
+  if (n_items <= 0) return 0;
+  if (G < 1 || H % G != 0 || (H / G) > 16 * nw || G > 65535) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+#define HK_HD(D) \
+  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, s);
+  HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
+#undef HK_HD
+  return HK_ERR_UNSUPPORTED;
+}
+
+HK_API int hk_attention_combine(const float* part_o, const float* part_ml, const int* first, const int* count,
+                                const int* row0, void* out, int n_tokens, int H, int G, int hd, int rows, void* stream) {
+  if (n_tokens <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int warps = 4;
+  const unsigned grid = (unsigned)(((long long)n_tokens * H + warps - 1) / warps);
+#define HK_HD(D) \
+  if (hd == D) { attention_combine_kernel<D><<<grid, warps * 32, 0, s>>>(part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows); return hk_launch_status(); }
+  HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
+#undef HK_HD
+  return HK_ERR_UNSUPPORTED;
+}

@@ -28,14 +28,15 @@ class StepContext:
     q_starts: List[int]
     q_lens: List[int]
     start_positions: List[int]
-    plans: Dict[int, object] = field(default_factory=dict)
+    plans: Dict[tuple, object] = field(default_factory=dict)
     plan_builder: Optional[object] = None
 
-    def attention_plan(self, page_tokens: int):
-        """The tiling of this batch for the flash attention kernel (built once per step and
-        page size); None sends attention to the generic kernel."""
+    def attention_plan(self, window: int, n_heads: int, n_kv_heads: int):
+        """The cut of this batch into work items for the flash attention kernel, built once per
+        step and (window, heads, groups); None sends attention to the generic kernel."""
         if self.plan_builder is None:
             return None
-        if page_tokens not in self.plans:
-            self.plans[page_tokens] = self.plan_builder(self, page_tokens)
-        return self.plans[page_tokens]
+        key = (window, n_heads, n_kv_heads)
+        if key not in self.plans:
+            self.plans[key] = self.plan_builder(self, window, n_heads, n_kv_heads)
+        return self.plans[key]

@@ -142,9 +142,9 @@ class Engine:
                                 max_requests, self.max_context)
         self.vocab = self.model.vocab
         self._requests: Dict[Hashable, int] = {}
-        self.plan_builder = None
         self.steps_run = 0
         self.stager = PinnedStager(self.device)
+        self.plan_builder = self._flash_plan if self.precision.compute == torch.bfloat16 else None
 
     # -- requests ----------------------------------------------------------------------------
     def open_request(self, request: Hashable) -> None:
@@ -172,6 +172,12 @@ class Engine:
 
     def free_pages(self) -> List[int]:
         return self.cache.books.free_pages()
+
+    def _flash_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int):
+        from ..csrc import attention_fast
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        return attention_fast.build_plan(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens, window,
+                                         n_heads, n_kv_heads, sms, self.stager.upload)
 
     # -- the step function -------------------------------------------------------------------
     def check_step(self, entries: Sequence[StepEntry]) -> None:

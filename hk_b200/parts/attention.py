@@ -91,7 +91,7 @@ class GQAAttention(Part):
         att = torch.empty_like(q)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
                             att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
-                            plan=ctx.attention_plan(cache.page_tokens))
+                            plan=ctx.attention_plan(self.window or 0, H, G) if xb.dtype == torch.bfloat16 else None)
         ops.gemm(att, self.w_o, residual, accumulate=True)
 
 

@@ -172,7 +172,7 @@ ATT_SHAPES = [(4, 2, 16, 4), (5, 1, 48, 16), (6, 2, 80, 8), (8, 2, 128, 16), (3,
               (2, 1, 112, 16)]
 
 
-def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=None):
+def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=None, sm_count=148, fixed_splits=0):
     """q_spans: per slot (first position, count) of the query rows; the cache holds lens[s] keys."""
     rng = np.random.default_rng(H * 1000 + hd + pt + window)
     k_pages, v_pages, bt, dk, dv = make_paged(rng, len(lens), lens, G, hd, pt, dtype)
@@ -197,6 +197,14 @@ def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=Non
     scale = 1.0 / math.sqrt(hd)
     out = torch.empty(n, H * hd, dtype=dtype, device=DEV)
     plan = None
+    if kernel != "generic":
+        from hk_b200.csrc import attention_fast
+        q_starts = [0]
+        for _, c in q_spans[:-1]:
+            q_starts.append(q_starts[-1] + c)
+        plan = attention_fast.build_plan(list(range(len(lens))), q_starts, [c for _, c in q_spans], [p0 for p0, _ in q_spans],
+                                         n, window, H, G, sm_count, lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV),
+                                         fixed_splits=fixed_splits)
     with ops().force(attention=kernel):
         ops().paged_attention(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), bt.to(DEV), pos_t.to(DEV), slot_t.to(DEV), out,
                               H, G, hd, pt, window, scale, plan=plan)
@@ -332,3 +340,56 @@ def test_gemm_swiglu_paired_layout(m, f, k):
         ops().gemm_swiglu(a.to(DEV), torch.cat([gate, up]).to(DEV), out3, 0)
     close(out2, want, torch.bfloat16, atol=2e-3)
     close(out3, want, torch.bfloat16, atol=2e-3)
+
+
+# ---- the flash attention kernel (bfloat16) -----------------------------------------------------
+
+FLASH_SHAPES = [(4, 2, 16, 4), (5, 1, 48, 16), (6, 2, 80, 8), (8, 2, 128, 16), (7, 7, 32, 32), (8, 1, 64, 16), (2, 1, 112, 16),
+                (32, 8, 128, 16), (12, 4, 96, 64), (40, 2, 64, 16)]
+
+
+@pytest.mark.parametrize("H,G,hd,pt", FLASH_SHAPES)
+@pytest.mark.parametrize("window", [0, 13, 100])
+def test_attention_flash_mixed_batch(H, G, hd, pt, window):
+    # a decode token deep in a long request, a portion that starts off-tile, a fresh request, a two-token portion
+    out, want, _ = attention_case("flash", torch.bfloat16, H, G, hd, pt, window, [300, 170, 5, 131],
+                                  [(299, 1), (37, 133), (0, 5), (129, 2)])
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+
+
+@pytest.mark.parametrize("H,G,hd,pt", [(8, 2, 128, 16), (5, 1, 48, 16), (4, 4, 64, 8)])
+@pytest.mark.parametrize("sm_count,fixed_splits", [(148, 0), (4000, 0), (148, 5), (148, 1)])
+@pytest.mark.parametrize("window", [0, 77])
+def test_attention_flash_decode_with_split_keys(H, G, hd, pt, sm_count, fixed_splits, window):
+    # decode only: one warp per CTA; few requests and long contexts are split along the keys and merged
+    out, want, _ = attention_case("flash", torch.bfloat16, H, G, hd, pt, window, [700, 64, 1, 129, 333],
+                                  [(699, 1), (63, 1), (0, 1), (128, 1), (332, 1)], sm_count=sm_count, fixed_splits=fixed_splits)
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+
+
+@pytest.mark.parametrize("j", [0, 15, 16, 63, 64, 65, 255, 256, 481])
+@pytest.mark.parametrize("fixed_splits", [0, 3])
+def test_attention_flash_finds_a_far_key(j, fixed_splits):
+    H, G, hd, pt = 4, 2, 64, 16
+    out, want, (q, dk, dv, slot, pos) = attention_case("flash", torch.bfloat16, H, G, hd, pt, 0, [500], [(499, 1)],
+                                                       spike=(0, 0, j, 1), fixed_splits=fixed_splits)
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    got = out.double().cpu().reshape(1, H, hd)
+    assert torch.allclose(got[0, 2], dv[0][j, 1], atol=0.05) and not torch.allclose(got[0, 0], dv[0][j, 1], atol=0.05)
+
+
+def test_attention_flash_window_edge_in_a_portion():
+    # rows at positions 90..99 with window 20: row 99 reads 80..99.  A dominant key at 80 is seen by row 99
+    # (the last row of the portion) and one at 79 is not, although rows 90..98 of the same tile do see 79.
+    H, G, hd, pt = 2, 1, 32, 8
+    out, want, (_, _, dv, _, _) = attention_case("flash", torch.bfloat16, H, G, hd, pt, 20, [100], [(90, 10)], spike=(9, 0, 80, 0))
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    assert torch.allclose(out.double().cpu().reshape(10, H, hd)[9, 0], dv[0][80, 0], atol=0.05)
+    out, want, (_, _, dv, _, _) = attention_case("flash", torch.bfloat16, H, G, hd, pt, 20, [100], [(90, 10)], spike=(9, 0, 79, 0))
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    assert not torch.allclose(out.double().cpu().reshape(10, H, hd)[9, 0], dv[0][79, 0], atol=0.2)
+
+
+def test_attention_flash_refuses_large_heads_and_generic_takes_them():
+    out, want, _ = attention_case(None, torch.bfloat16, 3, 3, 256, 16, 0, [40], [(0, 40)])
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
