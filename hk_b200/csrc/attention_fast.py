@@ -31,6 +31,7 @@ class FlashPlan:
     n_items: int
     items: torch.Tensor          # int32 [n_items, 8] on the device
     n_parts: int                 # partial results in scratch (0: none)
+    max_keys: int = 0            # the longest key range of an item
     first: Optional[torch.Tensor] = None   # per token: first partial, number of partials, row within the item
     count: Optional[torch.Tensor] = None
     row0: Optional[torch.Tensor] = None
@@ -41,9 +42,11 @@ def supported(hd: int, group: int) -> bool:
 
 
 def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
-               sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0) -> Optional[FlashPlan]:
+               sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0,
+               max_context: int = 0) -> Optional[FlashPlan]:
     """`upload(int32 array) -> device tensor`.  `fixed_splits` > 0 forces that many items per run
-    (a shape that does not change from step to step, for captured decode graphs)."""
+    (a shape that does not change from step to step, for captured decode graphs); `max_context`
+    then bounds the key range any later step can bring, which sizes the kernel's page-id buffer."""
     group = H // G
     nw = 1 if all(l == 1 for l in q_lens) else 4
     rows = 16 * nw
@@ -74,7 +77,7 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
         elif base_ctas >= 2 * sm_count:
             want = 1
         else:
-            want = max(1, min(-(-2 * sm_count // base_ctas), kv_len // 128))
+            want = max(1, min(-(-3 * sm_count // base_ctas), kv_len // 64, 32))
         chunk = -(-(-(-kv_len // want)) // TILE_N) * TILE_N
         n_split = fixed_splits if fixed_splits > 0 else max(1, -(-kv_len // chunk))
         if n_split == 1:
@@ -90,7 +93,10 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
             first[q_row0 + tq], count[q_row0 + tq], row0[q_row0 + tq] = n_parts, n_split, tq * group
         n_parts += n_split
     items = np.asarray(recs, dtype=np.int32).reshape(-1, 8)
-    plan = FlashPlan(nw, len(recs), upload(items), n_parts)
+    max_keys = max((r[5] - r[4] for r in recs), default=0)
+    if fixed_splits > 0 and max_context > 0:
+        max_keys = max(max_keys, -(-max_context // fixed_splits) + 2 * TILE_N)
+    plan = FlashPlan(nw, len(recs), upload(items), n_parts, max_keys)
     if n_parts:
         meta = upload(np.stack([first, count, row0]))
         plan.first, plan.count, plan.row0 = meta[0], meta[1], meta[2]
@@ -114,7 +120,8 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
     code = lib.hk_attention_flash(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]),
                                   _ptr(plan.items), plan.n_items, plan.nw, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
-                                  int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), stream)
+                                  int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
+                                  plan.max_keys // int(page_tokens) + 2, stream)
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "paged_attention (flash)")

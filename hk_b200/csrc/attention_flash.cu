@@ -75,6 +75,7 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);             // [2][TILE_N][LD]
   bf16* vs = ks + 2 * TILE_N * LD;                          // [2][TILE_N][LD]
+  int* tile_pages = reinterpret_cast<int*>(vs + 2 * TILE_N * LD);   // [2][TILE_N]
 
   const Item it = items[blockIdx.x];
   const int g = blockIdx.y;
@@ -118,18 +119,23 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   const int t_begin = it.kv_lo / TILE_N;
   const int t_end = (it.kv_hi + TILE_N - 1) / TILE_N;
 
+  // Page ids of a tile's keys are looked up once per tile (64 / page_tokens pages, or one page when pages
+  // are larger) into shared memory; the copy loop then only does arithmetic.
   auto load_tile = [&](int t, int stage) {
     bf16* kd = ks + stage * TILE_N * LD;
     bf16* vd = vs + stage * TILE_N * LD;
+    int* pg = tile_pages + stage * TILE_N;
+    for (int r = threadIdx.x; r < TILE_N; r += NW * 32) {
+      const int j = t * TILE_N + r;
+      pg[r] = (j >= it.kv_lo && j < it.kv_hi) ? bt[j / page_tokens] : -1;
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < TILE_N * CPR; idx += NW * 32) {
       const int r = idx / CPR, c = idx % CPR;
       const int j = t * TILE_N + r;
-      const bool ok = j >= it.kv_lo && j < it.kv_hi;
-      size_t off = 0;
-      if (ok) {
-        const int page = bt[j / page_tokens];
-        off = (((size_t)max(page, 0) * G + g) * page_tokens + (j % page_tokens)) * HD + c * 8;
-      }
+      const int page = pg[r];
+      const bool ok = page >= 0;
+      const size_t off = ok ? (((size_t)page * G + g) * page_tokens + (j % page_tokens)) * HD + c * 8 : 0;
       cp_async16(kd + r * LD + c * 8, k_pages + off, ok);
       cp_async16(vd + r * LD + c * 8, v_pages + off, ok);
     }
@@ -251,6 +257,212 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   }
 }
 
+// Decode variant, built for bandwidth: few rows (the heads of one group for one or a few tokens), long key
+// ranges.  The CTA's DW warps share the same 16 rows and split every DT-key tile among themselves, 16 keys
+// each; tiles come through a DS-stage cp.async ring (DS - 1 tiles in flight per CTA) and several small CTAs
+// share an SM, so enough bytes are in flight to keep HBM busy.  The item's page ids are read into shared
+// memory once, up front, so no tile waits on a block-table load.  The warps' softmax states are merged through
+// shared memory at the end, in warp order.
+constexpr int DW = 2;            // warps
+constexpr int DT = DW * 16;      // keys per tile
+constexpr int DS = 4;            // stages
+
+template <int HD>
+__global__ void __launch_bounds__(DW * 32)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                        const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
+                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
+                        int page_tokens, int window, float scale_log2, int pages_cap) {
+  constexpr int ROWS = 16;
+  constexpr int LD = HD + 8, CPR = HD / 8, KSTEPS = HD / 16;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* ks = reinterpret_cast<bf16*>(smem_raw);            // [DS][DT][LD]
+  bf16* vs = ks + DS * DT * LD;                            // [DS][DT][LD]
+  int* pages = reinterpret_cast<int*>(vs + DS * DT * LD);  // [pages_cap]
+
+  const Item it = items[blockIdx.x];
+  const int g = blockIdx.y;
+  const int group = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qr = lane >> 2, qt = lane & 3;
+  const int* bt = block_table + (size_t)it.slot * table_stride;
+
+  const int page_lo = it.kv_lo / page_tokens;
+  const int n_pages = it.kv_hi > it.kv_lo ? min((it.kv_hi - 1) / page_tokens - page_lo + 1, pages_cap) : 0;
+  for (int i = threadIdx.x; i < n_pages; i += DW * 32) pages[i] = bt[page_lo + i];
+
+  int row[2], pos[2], lo[2];
+  bool valid[2];
+  const bf16* qp[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    row[i] = qr + 8 * i;
+    int tq = row[i] / group;
+    valid[i] = tq < it.n_tokens;
+    if (!valid[i]) tq = 0;
+    pos[i] = it.pos0 + tq;
+    lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;
+    qp[i] = q + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
+  }
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int s = 0; s < KSTEPS; ++s) {
+    qf[s][0] = *reinterpret_cast<const uint32_t*>(qp[0] + s * 16 + 2 * qt);
+    qf[s][1] = *reinterpret_cast<const uint32_t*>(qp[1] + s * 16 + 2 * qt);
+    qf[s][2] = *reinterpret_cast<const uint32_t*>(qp[0] + s * 16 + 8 + 2 * qt);
+    qf[s][3] = *reinterpret_cast<const uint32_t*>(qp[1] + s * 16 + 8 + 2 * qt);
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+
+  const int t_begin = it.kv_lo / DT;
+  const int t_end = (it.kv_hi + DT - 1) / DT;
+  __syncthreads();   // page ids are in place
+
+  auto load_tile = [&](int t, int stage) {
+    bf16* kd = ks + stage * DT * LD;
+    bf16* vd = vs + stage * DT * LD;
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < DT * CPR; idx += DW * 32) {
+      const int r = idx / CPR, c = idx % CPR;
+      const int j = t * DT + r;
+      const int pi = j / page_tokens - page_lo;
+      const bool ok = j >= it.kv_lo && j < it.kv_hi && pi < n_pages;
+      const int page = ok ? pages[pi] : -1;
+      const bool use = page >= 0;
+      const size_t off = use ? (((size_t)page * G + g) * page_tokens + (j % page_tokens)) * HD + c * 8 : 0;
+      cp_async16(kd + r * LD + c * 8, k_pages + off, use);
+      cp_async16(vd + r * LD + c * 8, v_pages + off, use);
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < DS - 1; ++s) {
+    if (t_begin + s < t_end) load_tile(t_begin + s, s);
+    cp_async_commit();
+  }
+  for (int t = t_begin; t < t_end; ++t) {
+    const int stage = (t - t_begin) % DS;
+    cp_async_wait<DS - 2>();
+    __syncthreads();      // tile t has landed for everyone, and everyone is done with tile t - 1
+    if (t + DS - 1 < t_end) load_tile(t + DS - 1, (stage + DS - 1) % DS);
+    cp_async_commit();
+    const bf16* kt = ks + stage * DT * LD + warp * 16 * LD;   // this warp's 16 keys of the tile
+    const bf16* vt = vs + stage * DT * LD + warp * 16 * LD;
+    const int mi = lane >> 3, r8 = lane & 7;
+
+    float s[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t b[4];
+      ldmatrix_x4(b, kt + ((mi >> 1) * 8 + r8) * LD + kk * 16 + (mi & 1) * 8);
+      mma_bf16(s[0], qf[kk], b[0], b[1]);
+      mma_bf16(s[1], qf[kk], b[2], b[3]);
+    }
+    float mt[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int j = t * DT + warp * 16 + n * 8 + 2 * qt + (e & 1);
+        const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
+        s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
+        mt[i] = fmaxf(mt[i], s[n][e]);
+      }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mt[i] = fmaxf(mt[i], __shfl_xor_sync(0xffffffffu, mt[i], 1));
+      mt[i] = fmaxf(mt[i], __shfl_xor_sync(0xffffffffu, mt[i], 2));
+      const float mn = fmaxf(m[i], mt[i]);
+      msafe[i] = mn == -CUDART_INF_F ? 0.f : mn;
+      corr[i] = exp2f(m[i] - msafe[i]);
+      m[i] = mn;
+      l[i] *= corr[i];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+      o[n][0] *= corr[0];
+      o[n][1] *= corr[0];
+      o[n][2] *= corr[1];
+      o[n][3] *= corr[1];
+    }
+    uint32_t pf[4];
+    float p[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[h][e] = exp2f(s[h][e] - msafe[e >> 1]);
+        l[e >> 1] += p[h][e];
+      }
+    pf[0] = pack_bf16(p[0][0], p[0][1]);
+    pf[1] = pack_bf16(p[0][2], p[0][3]);
+    pf[2] = pack_bf16(p[1][0], p[1][1]);
+    pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vt + ((mi & 1) * 8 + r8) * LD + dp * 16 + (mi >> 1) * 8);
+      mma_bf16(o[2 * dp], pf, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the warps' states (the tile buffers are free now)
+  float* mo = reinterpret_cast<float*>(smem_raw);        // [DW][ROWS][HD]
+  float* mm = mo + DW * ROWS * HD;                       // [DW][ROWS]
+  float* ml = mm + DW * ROWS;                            // [DW][ROWS]
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    float* dst = mo + ((size_t)warp * ROWS + row[i]) * HD;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+      *reinterpret_cast<float2*>(dst + n * 8 + 2 * qt) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+    if (qt == 0) {
+      mm[warp * ROWS + row[i]] = m[i];
+      ml[warp * ROWS + row[i]] = l[i];
+    }
+  }
+  __syncthreads();
+  const size_t pbase = it.part < 0 ? 0 : ((size_t)it.part * G + g) * ROWS;
+  for (int idx = threadIdx.x; idx < ROWS * HD; idx += DW * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float mx = mm[r];
+#pragma unroll
+    for (int w = 1; w < DW; ++w) mx = fmaxf(mx, mm[w * ROWS + r]);
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < DW; ++w) {
+      const float mw = mm[w * ROWS + r];
+      const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mx);
+      acc += mo[((size_t)w * ROWS + r) * HD + d] * f;
+      lsum += ml[w * ROWS + r] * f;
+    }
+    if (it.part < 0) {
+      const int tq = r / group;
+      if (tq < it.n_tokens)
+        out[((size_t)(it.q_row0 + tq) * H + g * group + r % group) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    } else {
+      part_o[(pbase + r) * HD + d] = acc;
+      if (d == 0) *reinterpret_cast<float2*>(part_ml + (pbase + r) * 2) = make_float2(mx, lsum);
+    }
+  }
+}
+
 // One warp per (token, head): merges `count[t]` partials starting at `first[t]` (row `row0[t] + head % group`).
 // Tokens with count 0 were written directly by the main kernel.
 template <int HD>
@@ -295,7 +507,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 template <int HD, int NW>
 int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, cudaStream_t s) {
-  const size_t smem = (size_t)4 * TILE_N * (HD + 8) * sizeof(bf16);
+  const size_t smem = (size_t)4 * TILE_N * (HD + 8) * sizeof(bf16) + 2 * TILE_N * sizeof(int);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -310,27 +522,51 @@ int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, i
 }
 
 template <int HD>
+int launch_decode(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
+                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int pages_cap,
+                  cudaStream_t s) {
+  const size_t tiles = (size_t)2 * DS * DT * (HD + 8) * sizeof(bf16);
+  const size_t merge = (size_t)DW * 16 * (HD + 2) * sizeof(float);
+  const size_t smem = (tiles > merge ? tiles : merge) + (size_t)pages_cap * sizeof(int);
+  if (smem > 200 * 1024) return HK_ERR_UNSUPPORTED;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  dim3 grid((unsigned)n_items, (unsigned)G);
+  attention_decode_kernel<HD><<<grid, DW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
+                                                         (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
+                                                         scale_log2, pages_cap);
+  return hk_launch_status();
+}
+
+template <int HD>
 int launch_hd(int nw, const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
-              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, cudaStream_t s) {
-  if (nw == 1) return launch_flash<HD, 1>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, s);
+              void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, int pages_cap,
+              cudaStream_t s) {
+  if (nw == 1) return launch_decode<HD>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, pages_cap, s);
   if (nw == 4) return launch_flash<HD, 4>(q, kp, vp, bt, stride, items, n_items, out, part_o, part_ml, H, G, pt, window, scale_log2, s);
   return HK_ERR_UNSUPPORTED;
 }
 
 }  // namespace
 
-// items: device array of n_items records of 8 ints (see `Item`).  nw: warps per CTA (1 or 4); an item holds at
-// most (16 * nw) / (H / G) query tokens.  part_o [parts, G, 16*nw, hd] and part_ml [parts, G, 16*nw, 2] are
-// fp32 scratch for items with part >= 0.  scale_log2 = scale * log2(e).
+// items: device array of n_items records of 8 ints (see `Item`).  nw = 4: 64 rows per CTA, a warp per 16 rows;
+// nw = 1: the decode variant, 16 rows per CTA whose four warps split the keys.  An item holds at most
+// (16 * nw) / (H / G) query tokens.  part_o [parts, G, 16*nw, hd] and part_ml [parts, G, 16*nw, 2] are
+// fp32 scratch for items with part >= 0.  scale_log2 = scale * log2(e).  pages_cap: the most pages any item's key
+// range spans (the decode variant keeps that many page ids in shared memory).
 HK_API int hk_attention_flash(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                               int table_stride, const void* items, int n_items, int nw, void* out, float* part_o,
                               float* part_ml, int H, int G, int hd, int page_tokens, int window, float scale_log2,
-                              void* stream) {
+                              int pages_cap, void* stream) {
   if (n_items <= 0) return 0;
   if (G < 1 || H % G != 0 || (H / G) > 16 * nw || G > 65535) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
 #define HK_HD(D) \
-  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, s);
+  if (hd == D) return launch_hd<D>(nw, q, k_pages, v_pages, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens, window, scale_log2, pages_cap, s);
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;

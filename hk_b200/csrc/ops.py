@@ -60,6 +60,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Adds kernel launches made outside this module's wrappers (a replayed CUDA graph's nodes)."""
+    global _launches
+    _launches += n
+
+
 def _check(code: int, what: str, launches: int = 1) -> None:
     global _launches
     if code == 0:

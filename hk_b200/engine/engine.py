@@ -113,7 +113,7 @@ class Engine:
                  random_seed: Optional[int] = None, random_std: Optional[float] = None,
                  random_norm_std: float = 0.05, dtype="bfloat16", max_tokens: int = 8192,
                  page_tokens: int = 16, max_requests: int = 8, max_context: Optional[int] = None,
-                 max_batch_tokens: int = 8192, device: int = 0):
+                 max_batch_tokens: int = 8192, device: int = 0, decode_graphs: bool = True):
         self.device = _resolve_device(device)
         self.precision = Precision(parse_dtype(dtype), self.device)
         if config is None:
@@ -145,6 +145,9 @@ class Engine:
         self.steps_run = 0
         self.stager = PinnedStager(self.device)
         self.plan_builder = self._flash_plan if self.precision.compute == torch.bfloat16 else None
+        from .graphs import model_is_graph_safe
+        self.decode_graphs = bool(decode_graphs) and model_is_graph_safe(self.model)
+        self._graphs: Dict[int, object] = {}
 
     # -- requests ----------------------------------------------------------------------------
     def open_request(self, request: Hashable) -> None:
@@ -243,6 +246,13 @@ class Engine:
             q_starts.append(r)
             q_lens.append(m)
             r += m
+        if self.decode_graphs and n == len(entries) and all(list(e.want) == [0] for e in entries):
+            from .graphs import DecodeGraph
+            g = self._graphs.get(n)
+            if g is None:
+                g = self._graphs[n] = DecodeGraph(self, n)
+            self.steps_run += 1
+            return g.run(meta, slots, starts)
         meta_dev = self.stager.upload(meta)
         ctx = StepContext(self.precision, n, meta_dev[0], meta_dev[1], meta_dev[2], slots, q_starts, q_lens,
                           starts, plan_builder=self.plan_builder)

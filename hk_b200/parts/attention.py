@@ -27,6 +27,8 @@ from .position import RotaryEmbedding
 
 
 class GQAAttention(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
                  qk_norm_eps: Optional[float] = None, position: Optional[RotaryEmbedding] = None,
                  window: Optional[int] = None, scale: Optional[float] = None):

@@ -76,7 +76,13 @@ class Precision:
 
 
 class Part:
-    """Base of all parts.  Sub-parts are found through `children()`."""
+    """Base of all parts.  Sub-parts are found through `children()`.
+
+    `graph_safe`: the part's forward reads the step's batch only from the context's device
+    tensors (never from its host lists) and launches the same kernels for the same batch shape,
+    so a decode step through it can be captured in a CUDA graph.  False unless a part says so."""
+
+    graph_safe = False
 
     def children(self) -> Iterable["Part"]:
         return ()

@@ -10,6 +10,8 @@ from .base import Part, register_part
 
 
 class PreNormBlock(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, mixer_norm, mixer, ffn_norm, feed_forward):
         self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
 

@@ -16,6 +16,8 @@ from .base import MATRIX, ParamSpec, Part, Precision
 
 
 class TokenEmbedding(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, vocab: int, hidden: int, name: str):
         self.vocab, self.hidden, self.name = vocab, hidden, name
         self.table = None
@@ -31,6 +33,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, hidden: int, vocab: int, norm, name: str, tied_to: Optional[str] = None):
         self.hidden, self.vocab, self.norm, self.name, self.tied_to = hidden, vocab, norm, name, tied_to
         self.weight = None

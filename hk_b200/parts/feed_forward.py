@@ -13,6 +13,8 @@ from .base import MATRIX, ParamSpec, Part, Precision, register_part
 
 
 class SwiGLUFeedForward(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, hidden: int, intermediate: int, prefix: str):
         self.hidden, self.F, self.prefix = hidden, intermediate, prefix
         self.w_gate_up = self.w_down = None

@@ -11,6 +11,8 @@ from .base import VECTOR, ParamSpec, Part, Precision, register_part
 
 
 class RMSNorm(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, width: int, eps: float, weight_name: str):
         self.width = width
         self.eps = float(eps)

@@ -14,6 +14,8 @@ from .base import Part, Precision, register_part
 
 
 class RotaryEmbedding(Part):
+    graph_safe = True   # reads the batch from device tensors only
+
     def __init__(self, theta: float, rotary_dim: int, max_positions: int):
         if rotary_dim % 2 or rotary_dim < 2:
             raise ValueError(f"rotary width {rotary_dim} must be even and at least 2")
