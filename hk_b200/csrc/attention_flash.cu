@@ -16,6 +16,8 @@
 // Head sizes: multiples of 16 up to 128.  Any group size up to 16 * warps.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -583,4 +585,51 @@ HK_API int hk_attention_combine(const float* part_o, const float* part_ml, const
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
+}
+
+// ---- the entry point that allocates nothing (see attention_noalloc.h) -------------------------------------
+#include "attention_noalloc.h"
+
+// Scratch for the partial results, part of the library image: [n_parts][G][16][hd] values, then
+// [n_parts][G][16][2] (max, sum).  In host code this name is only a stand-in for the symbol; the device
+// address comes from cudaGetSymbolAddress below and is what the kernels are given.
+static __device__ __align__(256) float hk_noalloc_scratch[HK_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+HK_API int hk_attention_decode_noalloc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                       int table_stride, const void* items, int n_items, int n_parts, const int* first,
+                                       const int* count, const int* row0, void* out, int n_tokens, int H, int G, int hd,
+                                       int page_tokens, int window, float scale_log2, int pages_cap, void* stream) {
+  if (n_items <= 0 || n_tokens <= 0) return 0;
+  if (n_parts < 0 || G < 1 || hd < 1) return HK_ERR_UNSUPPORTED;
+  const size_t rows = 16;
+  const size_t need = (size_t)n_parts * G * rows * ((size_t)hd + 2) * sizeof(float);
+  if (need > HK_NOALLOC_SCRATCH_BYTES) return HK_ERR_SCRATCH_TOO_SMALL;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return HK_ERR_UNSUPPORTED;
+  float* scratch;
+  {
+    // set-up, once per device, with that device current: the array's address on this device
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      float* p = nullptr;
+      e = cudaGetSymbolAddress((void**)&p, hk_noalloc_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)n_parts * G * rows * hd;
+  int code = hk_attention_flash(q, k_pages, v_pages, block_table, table_stride, items, n_items, 1, out, part_o, part_ml, H, G,
+                                hd, page_tokens, window, scale_log2, pages_cap, stream);
+  if (code != 0 || n_parts == 0) return code;
+  return hk_attention_combine(part_o, part_ml, first, count, row0, out, n_tokens, H, G, hd, (int)rows, stream);
 }

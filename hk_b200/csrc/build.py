@@ -38,7 +38,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_smallm": "gemm_smallm.cu",
     "attention_flash": "attention_flash.cu",
 }
-HEADERS: List[str] = ["common.cuh"]
+HEADERS: List[str] = ["common.cuh", "attention_noalloc.h"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
