@@ -77,7 +77,7 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
         elif base_ctas >= 2 * sm_count:
             want = 1
         else:
-            want = max(1, min(-(-3 * sm_count // base_ctas), kv_len // 64, 32))
+            want = max(1, min(2 * sm_count // base_ctas, kv_len // 64, 32))
         chunk = -(-(-(-kv_len // want)) // TILE_N) * TILE_N
         n_split = fixed_splits if fixed_splits > 0 else max(1, -(-kv_len // chunk))
         if n_split == 1:
@@ -107,8 +107,13 @@ def _ptr(t):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
-def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan: FlashPlan) -> bool:
-    from . import ops
+def tma_decode_supported(hd: int, group: int, page_tokens: int) -> bool:
+    return hd in (64, 128) and group <= 16 and page_tokens >= 16 and page_tokens & (page_tokens - 1) == 0
+
+
+def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan: FlashPlan,
+        allow_tma: bool = True) -> bool:
+    from . import gemm_fast, ops
     if not supported(hd, H // G) or plan is None:
         return False
     lib = build.load("attention_flash")
@@ -118,10 +123,18 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
     if plan.n_parts:
         part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
-    code = lib.hk_attention_flash(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]),
-                                  _ptr(plan.items), plan.n_items, plan.nw, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
-                                  int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
-                                  plan.max_keys // int(page_tokens) + 2, stream)
+    code = _UNSUPPORTED
+    if plan.nw == 1 and allow_tma and tma_decode_supported(hd, H // G, int(page_tokens)):
+        code = lib.hk_attention_decode_tma(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), ctypes.c_longlong(k_pages.shape[0]), _ptr(block_table),
+            int(block_table.shape[1]), _ptr(plan.items), plan.n_items, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
+            int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)), plan.max_keys // int(page_tokens) + 2,
+            _ptr(gemm_fast.status_flag(q.device)), stream)
+    if code == _UNSUPPORTED:
+        code = lib.hk_attention_flash(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]),
+                                      _ptr(plan.items), plan.n_items, plan.nw, _ptr(out), _ptr(part_o), _ptr(part_ml), H, G, hd,
+                                      int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
+                                      plan.max_keys // int(page_tokens) + 2, stream)
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "paged_attention (flash)")

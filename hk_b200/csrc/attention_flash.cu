@@ -14,6 +14,7 @@
 // With splitting, each CTA writes an unnormalised partial (values, max, sum) to scratch and
 // `attention_combine_kernel` merges the partials of a (token, head) exactly, in split order.
 // Head sizes: multiples of 16 up to 128.  Any group size up to 16 * warps.
+#include <cuda.h>
 #include <math_constants.h>
 
 #include <mutex>
@@ -465,6 +466,294 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
   }
 }
 
+// Decode variant fed by TMA, for head sizes 64 and 128 and pages of 16 tokens or more (a power of two).
+// A (page, kv head) slab of the cache is contiguous, so a tile of 64 keys is a few boxes of box_rows keys; ONE
+// thread of a producer warp requests them with cp.async.bulk.tensor (a 3-d view [64 columns, rows, halves of
+// the head] so that a box brings all of a key's columns and lands as [half][row][128 bytes] with the 128-byte
+// swizzle), completion on a "full" mbarrier per stage.  The four consumer warps only compute: each takes 16 of
+// the tile's 64 keys, reads K and V through ldmatrix with the swizzle applied to the address, and releases the
+// stage on an "empty" mbarrier; there is no block-wide barrier inside the loop.  TS stages per CTA and two
+// CTAs per SM keep about 128 KB in flight per SM.  Boxes outside the item's key range are not requested; what
+// the stage then holds is masked (K) or finite and multiplied by zero (V: the stages are zeroed once at the
+// start).  Every wait is bounded; on time-out the CTA sets `status`, writes nothing and leaves.
+constexpr int TW = 4;             // consumer warps (a fifth warp produces)
+constexpr int TT = 64;            // keys per tile
+constexpr int TS = 3;             // stages
+constexpr uint32_t T_WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// false: gave up (this wait timed out, or another warp of the CTA already did)
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < T_WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__((TW + 1) * 32, 2)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const bf16* __restrict__ q, const int* __restrict__ block_table, int table_stride,
+                            const Item* __restrict__ items, bf16* __restrict__ out, float* __restrict__ part_o,
+                            float* __restrict__ part_ml, int H, int G, int page_tokens, int box_rows, int window,
+                            float scale_log2, int pages_cap, int* __restrict__ status) {
+  constexpr int ROWS = 16;
+  constexpr int KSTEPS = HD / 16;
+  constexpr int TILE_BYTES = TT * HD * 2;            // K (or V) of one stage
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint8_t* kbuf = base;                              // [TS][boxes][HALVES][box_rows][128 bytes]
+  uint8_t* vbuf = base + TS * TILE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(vbuf + TS * TILE_BYTES);   // [TS]
+  uint64_t* empty = full + TS;                                           // [TS]
+  int* abort_flag_s = reinterpret_cast<int*>(empty + TS);
+  int* pages = abort_flag_s + 2;                     // [pages_cap]
+  volatile int* abort_flag = abort_flag_s;
+
+  const Item it = items[blockIdx.x];
+  const int g = blockIdx.y;
+  const int group = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* bt = block_table + (size_t)it.slot * table_stride;
+
+  const int page_lo = it.kv_lo / page_tokens;
+  const int n_pages = it.kv_hi > it.kv_lo ? min((it.kv_hi - 1) / page_tokens - page_lo + 1, pages_cap) : 0;
+  for (int i = threadIdx.x; i < n_pages; i += (TW + 1) * 32) pages[i] = bt[page_lo + i];
+  // zero the V stages once: a box that is never requested must not leave NaN patterns to be multiplied by 0
+  for (int i = threadIdx.x; i < TS * TILE_BYTES / 16; i += (TW + 1) * 32) reinterpret_cast<uint4*>(vbuf)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TS; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], TW);
+    }
+    *abort_flag_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroes are ordered before the TMA writes
+  const int t_begin = it.kv_lo / TT;
+  const int t_end = (it.kv_hi + TT - 1) / TT;
+  __syncthreads();   // page ids, zeroes and barriers are in place
+
+  float o[HD / 8][4];
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  int row[2] = {0, 0};
+  const int qr = lane >> 2, qt = lane & 3;
+
+  if (warp == TW) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const int boxes = TT / box_rows;
+      const uint32_t box_bytes = (uint32_t)box_rows * HD * 2;
+      for (int t = t_begin; t < t_end; ++t) {
+        const int n = t - t_begin;
+        const int stage = n % TS;
+        if (n >= TS && !mbar_wait_bounded(&empty[stage], (uint32_t)((n / TS - 1) & 1), abort_flag)) break;
+        uint32_t bytes = 0;
+        for (int b = 0; b < boxes; ++b) {
+          const int j = t * TT + b * box_rows;
+          const int pi = j / page_tokens - page_lo;
+          if (j < it.kv_hi && j + box_rows > it.kv_lo && pi >= 0 && pi < n_pages && pages[pi] >= 0) bytes += 2u * box_bytes;
+        }
+        mbar_expect_tx(&full[stage], bytes);
+        for (int b = 0; b < boxes; ++b) {
+          const int j = t * TT + b * box_rows;
+          const int pi = j / page_tokens - page_lo;
+          if (!(j < it.kv_hi && j + box_rows > it.kv_lo && pi >= 0 && pi < n_pages && pages[pi] >= 0)) continue;
+          const int grow = (pages[pi] * G + g) * page_tokens + (j % page_tokens);    // row of the [rows, HD] view
+          tma_load_3d(kbuf + stage * TILE_BYTES + b * box_bytes, &map_k, &full[stage], 0, grow, 0);
+          tma_load_3d(vbuf + stage * TILE_BYTES + b * box_bytes, &map_v, &full[stage], 0, grow, 0);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    int pos[2], lo[2];
+    bool valid[2];
+    const bf16* qp[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      row[i] = qr + 8 * i;
+      int tq = row[i] / group;
+      valid[i] = tq < it.n_tokens;
+      if (!valid[i]) tq = 0;
+      pos[i] = it.pos0 + tq;
+      lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;
+      qp[i] = q + ((size_t)(it.q_row0 + tq) * H + g * group + row[i] % group) * HD;
+    }
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) {
+      qf[s][0] = *reinterpret_cast<const uint32_t*>(qp[0] + s * 16 + 2 * qt);
+      qf[s][1] = *reinterpret_cast<const uint32_t*>(qp[1] + s * 16 + 2 * qt);
+      qf[s][2] = *reinterpret_cast<const uint32_t*>(qp[0] + s * 16 + 8 + 2 * qt);
+      qf[s][3] = *reinterpret_cast<const uint32_t*>(qp[1] + s * 16 + 8 + 2 * qt);
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+
+    // this warp's 16 keys of a tile sit in box (warp * 16) / box_rows at rows (warp * 16) % box_rows ..
+    const int my_box = (warp * 16) / box_rows, my_row0 = (warp * 16) % box_rows;
+    const uint32_t box_bytes = (uint32_t)box_rows * HD * 2;
+    const uint32_t half_bytes = (uint32_t)box_rows * 128;
+    const int mi = lane >> 3, r8 = lane & 7;
+
+    for (int t = t_begin; t < t_end; ++t) {
+      const int n = t - t_begin;
+      const int stage = n % TS;
+      if (!mbar_wait_bounded(&full[stage], (uint32_t)((n / TS) & 1), abort_flag)) break;
+      const uint32_t kt = smem_u32(kbuf + stage * TILE_BYTES) + my_box * box_bytes;
+      const uint32_t vt = smem_u32(vbuf + stage * TILE_BYTES) + my_box * box_bytes;
+
+      float s[2][4];
+#pragma unroll
+      for (int nn = 0; nn < 2; ++nn)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nn][e] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        uint32_t b[4];
+        const int r = my_row0 + (mi >> 1) * 8 + r8;
+        const int d0 = kk * 16 + (mi & 1) * 8;
+        const uint32_t addr = kt + (d0 / 64) * half_bytes + r * 128 + ((((d0 % 64) >> 3) ^ (r & 7)) << 4);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(addr));
+        mma_bf16(s[0], qf[kk], b[0], b[1]);
+        mma_bf16(s[1], qf[kk], b[2], b[3]);
+      }
+      float mt[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int nn = 0; nn < 2; ++nn)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int j = t * TT + warp * 16 + nn * 8 + 2 * qt + (e & 1);
+          const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
+          s[nn][e] = ok ? s[nn][e] * scale_log2 : -CUDART_INF_F;
+          mt[i] = fmaxf(mt[i], s[nn][e]);
+        }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mt[i] = fmaxf(mt[i], __shfl_xor_sync(0xffffffffu, mt[i], 1));
+        mt[i] = fmaxf(mt[i], __shfl_xor_sync(0xffffffffu, mt[i], 2));
+        const float mn = fmaxf(m[i], mt[i]);
+        msafe[i] = mn == -CUDART_INF_F ? 0.f : mn;
+        corr[i] = exp2f(m[i] - msafe[i]);
+        m[i] = mn;
+        l[i] *= corr[i];
+      }
+#pragma unroll
+      for (int nn = 0; nn < HD / 8; ++nn) {
+        o[nn][0] *= corr[0];
+        o[nn][1] *= corr[0];
+        o[nn][2] *= corr[1];
+        o[nn][3] *= corr[1];
+      }
+      uint32_t pf[4];
+      float p[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[h][e] = exp2f(s[h][e] - msafe[e >> 1]);
+          l[e >> 1] += p[h][e];
+        }
+      pf[0] = pack_bf16(p[0][0], p[0][1]);
+      pf[1] = pack_bf16(p[0][2], p[0][3]);
+      pf[2] = pack_bf16(p[1][0], p[1][1]);
+      pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t b[4];
+        const int r = my_row0 + (mi & 1) * 8 + r8;
+        const int d0 = dp * 16 + (mi >> 1) * 8;
+        const uint32_t addr = vt + (d0 / 64) * half_bytes + r * 128 + ((((d0 % 64) >> 3) ^ (r & 7)) << 4);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(addr));
+        mma_bf16(o[2 * dp], pf, b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);   // this warp is done with the stage
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, 2);
+    return;            // nothing is written
+  }
+
+  // ---- merge the consumer warps' states through the (now idle) K stages
+  float* mo = reinterpret_cast<float*>(kbuf);            // [TW][ROWS][HD]
+  float* mm = mo + TW * ROWS * HD;                       // [TW][ROWS]
+  float* ml = mm + TW * ROWS;                            // [TW][ROWS]
+  if (warp < TW) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+      l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+      float* dst = mo + ((size_t)warp * ROWS + row[i]) * HD;
+#pragma unroll
+      for (int n = 0; n < HD / 8; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8 + 2 * qt) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+      if (qt == 0) {
+        mm[warp * ROWS + row[i]] = m[i];
+        ml[warp * ROWS + row[i]] = l[i];
+      }
+    }
+  }
+  __syncthreads();
+  const size_t pbase = it.part < 0 ? 0 : ((size_t)it.part * G + g) * ROWS;
+  for (int idx = threadIdx.x; idx < ROWS * HD; idx += (TW + 1) * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float mx = mm[r];
+#pragma unroll
+    for (int w = 1; w < TW; ++w) mx = fmaxf(mx, mm[w * ROWS + r]);
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < TW; ++w) {
+      const float mw = mm[w * ROWS + r];
+      const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mx);
+      acc += mo[((size_t)w * ROWS + r) * HD + d] * f;
+      lsum += ml[w * ROWS + r] * f;
+    }
+    if (it.part < 0) {
+      const int tq = r / group;
+      if (tq < it.n_tokens)
+        out[((size_t)(it.q_row0 + tq) * H + g * group + r % group) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+    } else {
+      part_o[(pbase + r) * HD + d] = acc;
+      if (d == 0) *reinterpret_cast<float2*>(part_ml + (pbase + r) * 2) = make_float2(mx, lsum);
+    }
+  }
+}
+
 // One warp per (token, head): merges `count[t]` partials starting at `first[t]` (row `row0[t] + head % group`).
 // Tokens with count 0 were written directly by the main kernel.
 template <int HD>
@@ -585,6 +874,83 @@ HK_API int hk_attention_combine(const float* part_o, const float* part_ml, const
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
+}
+
+// ---- host side of the TMA decode variant -----------------------------------------------------------------
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// The cache pages of one layer, a bf16 matrix [rows, hd], seen as [64 columns, rows, hd / 64 halves]; a box
+// takes 64 columns x box_rows rows x all halves and lands as [half][row][128 bytes] with the 128-byte swizzle.
+bool make_page_map(CUtensorMap* map, const void* ptr, unsigned long long rows, int hd, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(hd / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)hd * 2, 128u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(hd / 64)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* bt, int stride, const void* items,
+                      int n_items, void* out, float* part_o, float* part_ml, int H, int G, int pt, int box_rows, int window,
+                      float scale_log2, int pages_cap, int* status, cudaStream_t s) {
+  const size_t smem = 1024 + (size_t)2 * TS * TT * HD * 2 + 2 * TS * sizeof(uint64_t) + 8 + (size_t)pages_cap * sizeof(int);
+  if (smem > 110 * 1024) return HK_ERR_UNSUPPORTED;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  dim3 grid((unsigned)n_items, (unsigned)G);
+  attention_decode_tma_kernel<HD><<<grid, (TW + 1) * 32, smem, s>>>(mk, mv, (const bf16*)q, bt, stride, (const Item*)items, (bf16*)out,
+                                                             part_o, part_ml, H, G, pt, box_rows, window, scale_log2, pages_cap,
+                                                             status);
+  return hk_launch_status();
+}
+
+}  // namespace
+
+// The decode variant fed by TMA.  Same arguments as hk_attention_flash with nw = 1, plus the number of pages of
+// the cache tensors and a device status word (set to 2 if a wait times out).  Refuses (HK_ERR_UNSUPPORTED) head
+// sizes other than 64 and 128, pages under 16 tokens or not a power of two, groups above 16 heads.
+HK_API int hk_attention_decode_tma(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
+                                   const int* block_table, int table_stride, const void* items, int n_items, void* out,
+                                   float* part_o, float* part_ml, int H, int G, int hd, int page_tokens, int window,
+                                   float scale_log2, int pages_cap, int* status, void* stream) {
+  if (n_items <= 0) return 0;
+  if (G < 1 || H % G != 0 || (H / G) > 16 || G > 65535) return HK_ERR_UNSUPPORTED;
+  if ((hd != 64 && hd != 128) || page_tokens < 16 || (page_tokens & (page_tokens - 1))) return HK_ERR_UNSUPPORTED;
+  if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return HK_ERR_UNSUPPORTED;
+  const int box_rows = page_tokens < TT ? page_tokens : TT;
+  const unsigned long long rows = (unsigned long long)num_pages * G * page_tokens;
+  CUtensorMap mk, mv;
+  if (!make_page_map(&mk, k_pages, rows, hd, box_rows) || !make_page_map(&mv, v_pages, rows, hd, box_rows)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 64)
+    return launch_decode_tma<64>(mk, mv, q, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens,
+                                 box_rows, window, scale_log2, pages_cap, status, s);
+  return launch_decode_tma<128>(mk, mv, q, block_table, table_stride, items, n_items, out, part_o, part_ml, H, G, page_tokens,
+                                box_rows, window, scale_log2, pages_cap, status, s);
 }
 
 // ---- the entry point that allocates nothing (see attention_noalloc.h) -------------------------------------

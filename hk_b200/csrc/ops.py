@@ -84,7 +84,8 @@ _forced = {"gemm": None, "attention": None}
 @contextlib.contextmanager
 def force(gemm: Optional[str] = None, attention: Optional[str] = None):
     """Pins the kernel family inside the block: gemm in {'generic','tc','smallm'},
-    attention in {'generic','flash'}.  A pinned kernel that refuses the shape raises."""
+    attention in {'generic','flash','flash_cp'} ('flash_cp': the flash kernels without the TMA-fed decode
+    variant).  A pinned kernel that refuses the shape raises."""
     old = dict(_forced)
     if gemm is not None:
         _forced["gemm"] = gemm
@@ -272,7 +273,8 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
     choice = _forced["attention"]
     if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None:
         from . import attention_fast
-        if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan):
+        if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
+                              allow_tma=choice != "flash_cp"):
             return
         if choice is not None:
             raise KernelError(f"paged_attention: the '{choice}' kernel refuses head_dim={hd} page_tokens={page_tokens}")

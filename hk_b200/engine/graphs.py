@@ -39,9 +39,9 @@ class DecodeGraph:
 
     # -- attention plans over static buffers ---------------------------------------------------
     def _splits(self, n_kv_heads: int) -> int:
-        # enough CTAs to fill every SM three times over; at most 32 splits (the reference stops at 16:
-        # src/cuda/engine.zig:96-101)
-        return max(1, min(32, -(-3 * self.sms // (self.batch * n_kv_heads))))
+        # as many CTAs as are resident at once (two per SM), rounded down so that no second, thin wave
+        # follows; at most 32 splits (the reference stops at 16: src/cuda/engine.zig:96-101)
+        return max(1, min(32, 2 * self.sms // (self.batch * n_kv_heads)))
 
     def _build_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int):
         from ..csrc import attention_fast

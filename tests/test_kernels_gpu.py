@@ -357,14 +357,20 @@ def test_attention_flash_mixed_batch(H, G, hd, pt, window):
     close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
 
 
-@pytest.mark.parametrize("H,G,hd,pt", [(8, 2, 128, 16), (5, 1, 48, 16), (4, 4, 64, 8)])
+@pytest.mark.parametrize("kernel", ["flash", "flash_cp"])
+@pytest.mark.parametrize("H,G,hd,pt", [(8, 2, 128, 16), (5, 1, 48, 16), (4, 4, 64, 8), (32, 8, 128, 16), (6, 2, 64, 32), (4, 1, 128, 64),
+                                       (16, 1, 64, 128)])
 @pytest.mark.parametrize("sm_count,fixed_splits", [(148, 0), (4000, 0), (148, 5), (148, 1)])
 @pytest.mark.parametrize("window", [0, 77])
-def test_attention_flash_decode_with_split_keys(H, G, hd, pt, sm_count, fixed_splits, window):
-    # decode only: one warp per CTA; few requests and long contexts are split along the keys and merged
-    out, want, _ = attention_case("flash", torch.bfloat16, H, G, hd, pt, window, [700, 64, 1, 129, 333],
+def test_attention_flash_decode_with_split_keys(kernel, H, G, hd, pt, sm_count, fixed_splits, window):
+    # decode only: 16 rows per CTA, warps split the keys of a tile; few requests and long contexts are also
+    # split along the keys among CTAs and merged.  'flash' takes the TMA-fed variant where it applies
+    # (head size 64/128, pages of 16+ tokens), 'flash_cp' always the cp.async one.
+    out, want, _ = attention_case(kernel, torch.bfloat16, H, G, hd, pt, window, [700, 64, 1, 129, 333],
                                   [(699, 1), (63, 1), (0, 1), (128, 1), (332, 1)], sm_count=sm_count, fixed_splits=fixed_splits)
     close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    from hk_b200.csrc import gemm_fast
+    gemm_fast.check_status(torch.device(DEV))
 
 
 @pytest.mark.parametrize("j", [0, 15, 16, 63, 64, 65, 255, 256, 481])
