@@ -556,6 +556,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroes are ordered before the TMA writes
   const int t_begin = it.kv_lo / TT;
   const int t_end = (it.kv_hi + TT - 1) / TT;
+  // All of the above read only what the host wrote before the step (items, block table); the queries and this
+  // step's keys and values come from the kernel before.
+  pdl_wait();
   __syncthreads();   // page ids, zeroes and barriers are in place
 
   float o[HD / 8][4];
@@ -704,6 +707,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   }
   __syncthreads();
+  pdl_launch_dependents();   // the keys are read: the next kernel may move in
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(status, 2);
     return;            // nothing is written
@@ -761,6 +765,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
                                          const int* __restrict__ first, const int* __restrict__ count,
                                          const int* __restrict__ row0, bf16* __restrict__ out, int n_tokens, int H, int G,
                                          int rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= n_tokens * H) return;
@@ -870,7 +876,7 @@ HK_API int hk_attention_combine(const float* part_o, const float* part_ml, const
   const int warps = 4;
   const unsigned grid = (unsigned)(((long long)n_tokens * H + warps - 1) / warps);
 #define HK_HD(D) \
-  if (hd == D) { attention_combine_kernel<D><<<grid, warps * 32, 0, s>>>(part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows); return hk_launch_status(); }
+  if (hd == D) return hk_launch(attention_combine_kernel<D>, dim3(grid), dim3(warps * 32), 0, s, part_o, part_ml, first, count, row0, (bf16*)out, n_tokens, H, G, rows);
   HK_HD(16) HK_HD(32) HK_HD(48) HK_HD(64) HK_HD(80) HK_HD(96) HK_HD(112) HK_HD(128)
 #undef HK_HD
   return HK_ERR_UNSUPPORTED;
@@ -922,10 +928,8 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
     configured = smem;
   }
   dim3 grid((unsigned)n_items, (unsigned)G);
-  attention_decode_tma_kernel<HD><<<grid, (TW + 1) * 32, smem, s>>>(mk, mv, (const bf16*)q, bt, stride, (const Item*)items, (bf16*)out,
-                                                             part_o, part_ml, H, G, pt, box_rows, window, scale_log2, pages_cap,
-                                                             status);
-  return hk_launch_status();
+  return hk_launch(attention_decode_tma_kernel<HD>, grid, dim3((TW + 1) * 32), smem, s, mk, mv, (const bf16*)q, bt, stride,
+                       (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, pages_cap, status);
 }
 
 }  // namespace

@@ -27,6 +27,8 @@ template <typename T, int PER>
 __global__ void embedding_vec_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                      int d, int vocab) {
   constexpr int E = 16 / sizeof(T);   // elements per 16-byte load
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -60,9 +62,9 @@ HK_API int hk_embedding(const void* table, int table_dtype, const int* ids, floa
     const int e = table_dtype == HK_F32 ? 4 : 8;
     if (d % e == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0 && d / e <= 4 * 256) {
       if (table_dtype == HK_F32)
-        embedding_vec_kernel<float, 4><<<n, 256, 0, s>>>((const float*)table, ids, out, d, vocab);
+        return hk_launch(embedding_vec_kernel<float, 4>, dim3(n), dim3(256), 0, s, (const float*)table, ids, out, d, vocab);
       else if (table_dtype == HK_BF16)
-        embedding_vec_kernel<bf16, 4><<<n, 256, 0, s>>>((const bf16*)table, ids, out, d, vocab);
+        return hk_launch(embedding_vec_kernel<bf16, 4>, dim3(n), dim3(256), 0, s, (const bf16*)table, ids, out, d, vocab);
       else
         return HK_ERR_UNSUPPORTED;
       return hk_launch_status();
@@ -119,19 +121,21 @@ rms_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, co
   __shared__ float warp_part[8];
   __shared__ float inv_s;
   const int r = blockIdx.x;
-  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
   const float4* wv = reinterpret_cast<const float4*>(w);
   const int chunks = d >> 2;
   float4 v[PER], g[PER];
+  pdl_launch_dependents();
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {     // the norm's weight does not depend on the kernel before
+    const int c = threadIdx.x + k * 256;
+    if (c < chunks) g[k] = wv[c];
+  }
+  pdl_wait();
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
     const int c = threadIdx.x + k * 256;
-    if (c < chunks) {
-      v[k] = src[c];
-      g[k] = wv[c];
-    } else {
-      v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+    v[k] = c < chunks ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float ss = 0.f;
 #pragma unroll
@@ -173,12 +177,10 @@ template <int PER>
 static int rms_norm_vec(const float* x, const float* w, const int* rows, void* out, int out_dtype, int n_out, int d, float eps,
                         cudaStream_t s) {
   if (out_dtype == HK_F32)
-    rms_norm_vec_kernel<float, PER><<<n_out, 256, 0, s>>>(x, w, rows, (float*)out, d, eps);
-  else if (out_dtype == HK_BF16)
-    rms_norm_vec_kernel<bf16, PER><<<n_out, 256, 0, s>>>(x, w, rows, (bf16*)out, d, eps);
-  else
-    return HK_ERR_UNSUPPORTED;
-  return hk_launch_status();
+    return hk_launch(rms_norm_vec_kernel<float, PER>, dim3(n_out), dim3(256), 0, s, x, w, rows, (float*)out, d, eps);
+  if (out_dtype == HK_BF16)
+    return hk_launch(rms_norm_vec_kernel<bf16, PER>, dim3(n_out), dim3(256), 0, s, x, w, rows, (bf16*)out, d, eps);
+  return HK_ERR_UNSUPPORTED;
 }
 
 HK_API int hk_rms_norm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
@@ -222,6 +224,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
     int write_kv) {
   __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
+  pdl_launch_dependents();
+  pdl_wait();
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int heads_total = H + (write_kv ? 2 * G : 0);
   long long item = (long long)blockIdx.x * QKR_WARPS + wid;
@@ -285,16 +289,14 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
   long long items = (long long)n * (H + (write_kv ? 2 * G : 0));
   unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
   if (dtype == HK_F32)
-    qk_norm_rope_kv_write_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
-        qkv, (float*)q_out, q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table,
-        table_stride, (float*)k_pages, (float*)v_pages, n, H, G, hd, page_tokens, write_kv);
-  else if (dtype == HK_BF16)
-    qk_norm_rope_kv_write_kernel<bf16><<<blocks, QKR_WARPS * 32, 0, s>>>(
-        qkv, (bf16*)q_out, q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table,
-        table_stride, (bf16*)k_pages, (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv);
-  else
-    return HK_ERR_UNSUPPORTED;
-  return hk_launch_status();
+    return hk_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (float*)q_out, q_w,
+                         k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
+                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv);
+  if (dtype == HK_BF16)
+    return hk_launch(qk_norm_rope_kv_write_kernel<bf16>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
+                         k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
+                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv);
+  return HK_ERR_UNSUPPORTED;
 }
 
 // ----------------------------------------------------------------------------- swiglu
@@ -302,6 +304,8 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
 // `block` gates followed by the matching `block` ups (block == F: all gates, then all ups).
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block) {
+  pdl_launch_dependents();
+  pdl_wait();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   long long t = i / F;
@@ -318,11 +322,7 @@ HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, in
   cudaStream_t s = (cudaStream_t)stream;
   long long total = (long long)n * F;
   unsigned blocks = (unsigned)((total + 255) / 256);
-  if (out_dtype == HK_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, s>>>(gu, (float*)out, total, F, block);
-  else if (out_dtype == HK_BF16)
-    swiglu_kernel<bf16><<<blocks, 256, 0, s>>>(gu, (bf16*)out, total, F, block);
-  else
-    return HK_ERR_UNSUPPORTED;
-  return hk_launch_status();
+  if (out_dtype == HK_F32) return hk_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, gu, (float*)out, total, F, block);
+  if (out_dtype == HK_BF16) return hk_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, gu, (bf16*)out, total, F, block);
+  return HK_ERR_UNSUPPORTED;
 }

@@ -1,7 +1,8 @@
 """Choice among the bfloat16 tensor-core matrix products.
 
-  * up to 64 rows (decode): the weight-streaming mma.sync kernel (`gemm_smallm.cu`);
-  * more rows (prefill, mixed batches): the persistent tcgen05 kernel (`gemm_tc.cu`).
+  * up to 16 rows (small decode batches): the weight-streaming mma.sync kernel (`gemm_smallm.cu`);
+  * more rows (larger decode batches, prefill, mixed batches): the persistent tcgen05 kernel
+    (`gemm_tc.cu`), cutting K into slices when the output has fewer tiles than the GPU has SMs.
 The choice depends on the shape alone.  Shapes both refuse (K not a multiple of 8, unaligned
 operands) go to the generic kernel.
 """
@@ -15,7 +16,8 @@ import torch
 from . import build
 
 _UNSUPPORTED = 100001
-SMALL_M = 64
+SMALL_M = 64          # the most rows the weight-streaming kernel takes
+SMALL_M_AUTO = 16     # up to here it is chosen; above, the tcgen05 kernel with K slices streams better
 _status = {}
 _sm_count = {}
 
@@ -66,6 +68,21 @@ def row_tiles(M: int, N: int, device) -> int:
     return rt
 
 
+def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
+    """Tile width and number of K slices for the tcgen05 kernel.  Wide tiles when they still fill the SMs;
+    with fewer output tiles than SMs (few rows: decode batches, narrow outputs) K is cut into slices so that
+    every SM streams a share of the weights."""
+    m_tiles = -(-M // 128)
+    if bn == 0:
+        bn = 256 if N >= 256 and m_tiles * -(-N // 256) >= sms // 2 else 128
+    tiles = m_tiles * -(-N // bn)
+    k_blocks = -(-K // 64)
+    splits = 1
+    if tiles < sms:
+        splits = max(1, min(sms // tiles, k_blocks // 8))
+    return bn, splits
+
+
 def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     """out (fp32) = a w^T (+ out).  Returns False when no tensor-core kernel takes the shape."""
     from . import ops
@@ -73,7 +90,7 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     N = w.shape[0]
     if not _aligned(a, w):
         return False
-    if choice == "smallm" or (choice is None and M <= SMALL_M):
+    if choice == "smallm" or (choice is None and M <= SMALL_M_AUTO):
         if M > SMALL_M:
             return False
         lib = build.load("gemm_smallm")
@@ -84,9 +101,10 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
         ops._check(code, "gemm (small-M)")
         return True
     lib = build.load("gemm_tc")
-    bn = 256 if N >= 256 and -(-M // 128) * -(-N // 256) >= _sms(a.device) // 2 else 128
+    bn, splits = tc_config(M, N, K, _sms(a.device))
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else None
     code = lib.hk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(N), 1 if accumulate else 0, bn,
-                          _ptr(status_flag(a.device)), _stream())
+                          splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "gemm (tcgen05)")
@@ -102,8 +120,10 @@ def run_swiglu(a, w_paired, out) -> bool:
     if not _aligned(a, w_paired) or N % 256 or out.shape[1] % 8:
         return False
     lib = build.load("gemm_tc")
+    _, splits = tc_config(M, N, K, _sms(a.device), bn=256)
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else None
     code = lib.hk_gemm_tc(_ptr(a), _ptr(w_paired), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2, 256,
-                          _ptr(status_flag(a.device)), _stream())
+                          splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "gemm+swiglu (tcgen05)")

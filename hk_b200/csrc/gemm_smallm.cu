@@ -79,7 +79,10 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
         }
   };
 
+  // The weights do not depend on the kernel before: the first chunk is on its way before this kernel waits
+  // for that kernel's output (the activations).
   if (c_begin < c_end) load_w(c_begin);
+  pdl_wait();
   for (int c = c_begin; c < c_end; ++c) {
     uint4 cur[RT][2][2];
 #pragma unroll
@@ -145,10 +148,10 @@ int launch(const void* a, const void* w, float* out, int M, int N, int K, long l
   }
   const unsigned grid = (unsigned)((N + RT * 16 - 1) / (RT * 16));
   if (add)
-    gemm_smallm_kernel<MT, RT, true><<<grid, SM_WARPS * 32, smem, s>>>((const bf16*)a, (const bf16*)w, out, M, N, K, ldo);
-  else
-    gemm_smallm_kernel<MT, RT, false><<<grid, SM_WARPS * 32, smem, s>>>((const bf16*)a, (const bf16*)w, out, M, N, K, ldo);
-  return hk_launch_status();
+    return hk_launch_pdl(gemm_smallm_kernel<MT, RT, true>, dim3(grid), dim3(SM_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w,
+                         out, M, N, K, ldo);
+  return hk_launch_pdl(gemm_smallm_kernel<MT, RT, false>, dim3(grid), dim3(SM_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w,
+                       out, M, N, K, ldo);
 }
 
 }  // namespace

@@ -124,7 +124,7 @@ struct SharedStorage {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-               int M, int N, int K, long long ldo, int* __restrict__ status) {
+               int M, int N, int K, long long ldo, int splits, float* __restrict__ partial, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   using Storage = SharedStorage<BN, STAGES>;
   Storage& sm = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -132,8 +132,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int k_blocks = (K + BK - 1) / BK;
+  // With splits > 1 a work item is (output tile, slice of K); slice s of every tile comes before slice s + 1
+  // of any, so the CTAs running together read different weights.  Each item stores its fp32 partial to
+  // partial[s][M][N]; a second kernel adds the slices in order.
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total_tiles = mn_tiles * splits;
+  const int k_blocks_all = (K + BK - 1) / BK;
   constexpr uint32_t TMEM_COLS = 2 * BN;   // 256 or 512: a power of two >= 32
   constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
 
@@ -165,8 +169,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int mn = tile % mn_tiles, ks = tile / mn_tiles;
+        const int m0 = (mn % m_tiles) * BM, n0 = (mn / m_tiles) * BN;
+        const int kb0 = (int)((long long)k_blocks_all * ks / splits), kb1 = (int)((long long)k_blocks_all * (ks + 1) / splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sm.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&sm.full[stage], STAGE_BYTES);
           tma_load_2d(sm.a[stage], &map_a, &sm.full[stage], kb * BK, m0);
@@ -190,7 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!mbar_wait(&sm.tmem_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int ks = tile / mn_tiles;
+        const int kb0 = (int)((long long)k_blocks_all * ks / splits), kb1 = (int)((long long)k_blocks_all * (ks + 1) / splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sm.full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint64_t da = make_smem_desc(smem_u32(sm.a[stage]));
@@ -198,7 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance both start addresses by 32 bytes (16 bf16) inside the swizzled row
-            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&sm.empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -214,12 +222,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       const uint32_t use = (uint32_t)(local >> 1);
-      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+      const int mn = tile % mn_tiles, ks = tile / mn_tiles;
+      const int m0 = (mn % m_tiles) * BM, n0 = (mn / m_tiles) * BN;
       if (!mbar_wait(&sm.tmem_full[buf], use & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-      if (EPI == EPI_SWIGLU) {
+      if (splits > 1) {
+        // a slice's partial sum, fp32 [M, N]
+        float* o = partial + ((size_t)ks * M + row) * N + n0;
+        const int n_out = N - n0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + (uint32_t)c0, v);
+          tmem_ld_wait();
+          if (row < M) {
+            if (c0 + 32 <= n_out && (N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(o + c0 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                     __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < n_out) o[c0 + j] = __uint_as_float(v[j]);
+            }
+          }
+        }
+      } else if (EPI == EPI_SWIGLU) {
         // columns [0, BN/2) are gates, [BN/2, BN) the matching ups; output columns (n0 / 2) + c
         bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + (n0 >> 1);
         const int n_out = (N >> 1) - (n0 >> 1);
@@ -340,8 +370,37 @@ int sm_count() {
   return n;
 }
 
+// Adds the K slices of a split product in slice order.  mode 0: out fp32 = sum; 1: out fp32 += sum;
+// 2: out bf16 [M, N/2] = silu(gate) * up over the paired layout (blocks of 128 gates then their 128 ups).
+template <int MODE>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int M, int N, long long ldo,
+                                     int splits) {
+  const long long total = MODE == 2 ? (long long)M * (N / 2) : (long long)M * N;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t slice = (size_t)M * N;
+  if (MODE == 2) {
+    const int F = N / 2;
+    const int m = (int)(i / F), j = (int)(i % F);
+    const size_t gi = (size_t)m * N + (size_t)(j / 128) * 256 + (j % 128);
+    float gsum = 0.f, usum = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      gsum += partial[s * slice + gi];
+      usum += partial[s * slice + gi + 128];
+    }
+    reinterpret_cast<bf16*>(out)[(size_t)m * ldo + j] = __float2bfloat16_rn(gsum / (1.0f + __expf(-gsum)) * usum);
+  } else {
+    const int m = (int)(i / N), n = (int)(i % N);
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) sum += partial[s * slice + i];
+    float* o = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+    *o = MODE == 1 ? *o + sum : sum;
+  }
+}
+
 template <int BN, int STAGES, int EPI>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int* status, cudaStream_t s) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int splits, float* partial,
+           int* status, cudaStream_t s) {
   static bool configured = false;
   const size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
   if (!configured) {
@@ -349,9 +408,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tc_kernel<BN, STAGES, EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, status);
+  gemm_tc_kernel<BN, STAGES, EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, splits, partial, status);
+  int code = hk_launch_status();
+  if (code != 0 || splits <= 1) return code;
+  const long long total = EPI == EPI_SWIGLU ? (long long)M * (N / 2) : (long long)M * N;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  splitk_reduce_kernel<EPI><<<blocks, 256, 0, s>>>(partial, out, M, N, ldo, splits);
   return hk_launch_status();
 }
 
@@ -361,22 +425,25 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
 // silu(gate) * up with w's rows laid out [128 gate | 128 up] per 256-row tile.  `status` is a device int
 // that a timed-out wait sets to 1 (the caller reads it when it next synchronises).
 // Requirements (else HK_ERR_UNSUPPORTED): K % 8 == 0, a and w 16-byte aligned, for epilogue 2 N % 256 == 0.
+// splits > 1 cuts K into that many slices computed by different CTAs (for few output tiles: decode batches);
+// `partial` must then hold splits * M * N floats of scratch.
 HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
-                      int* status, void* stream) {
+                      int splits, float* partial, int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
   if (epilogue == EPI_SWIGLU && ((N & 255) || bn != 256)) return HK_ERR_UNSUPPORTED;
   if (bn != 128 && bn != 256) return HK_ERR_UNSUPPORTED;
+  if (splits < 1 || splits > (K + BK - 1) / BK || (splits > 1 && partial == nullptr)) return HK_ERR_UNSUPPORTED;
   CUtensorMap ma, mw;
   if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, N, K, bn)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   if (bn == 256) {
-    if (epilogue == EPI_STORE) return launch<256, 4, EPI_STORE>(ma, mw, out, M, N, K, ldo, status, s);
-    if (epilogue == EPI_ADD) return launch<256, 4, EPI_ADD>(ma, mw, out, M, N, K, ldo, status, s);
-    if (epilogue == EPI_SWIGLU) return launch<256, 4, EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, status, s);
+    if (epilogue == EPI_STORE) return launch<256, 4, EPI_STORE>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
+    if (epilogue == EPI_ADD) return launch<256, 4, EPI_ADD>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
+    if (epilogue == EPI_SWIGLU) return launch<256, 4, EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
   } else {
-    if (epilogue == EPI_STORE) return launch<128, 6, EPI_STORE>(ma, mw, out, M, N, K, ldo, status, s);
-    if (epilogue == EPI_ADD) return launch<128, 6, EPI_ADD>(ma, mw, out, M, N, K, ldo, status, s);
+    if (epilogue == EPI_STORE) return launch<128, 6, EPI_STORE>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
+    if (epilogue == EPI_ADD) return launch<128, 6, EPI_ADD>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
   }
   return HK_ERR_UNSUPPORTED;
 }

@@ -164,7 +164,7 @@ def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, bloc
     M, F = out.shape
     if a.shape[0] != M or w_paired.shape != (2 * F, a.shape[1]):
         raise KernelError("gemm_swiglu: shapes do not fit")
-    if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc") and M > 64:
+    if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc") and (M > 16 or _forced["gemm"] == "tc"):
         from . import gemm_fast
         if block == gemm_fast.PAIR and gemm_fast.run_swiglu(a, w_paired, out):
             return

@@ -79,6 +79,9 @@ class GQAAttention(Part):
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True) -> None:
         n = xb.shape[0]
         H, G, hd = self.H, self.G, self.hd
+        # the attention work items are uploaded before any kernel of this layer is launched (kernels may start
+        # ahead of their predecessor and read such host-written tables early)
+        plan = ctx.attention_plan(self.window or 0, H, G) if xb.dtype == torch.bfloat16 else None
         qkv = torch.empty((n, (H + 2 * G) * hd), dtype=torch.float32, device=xb.device)
         ops.gemm(xb, self.w_qkv, qkv)
         q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)
@@ -93,7 +96,7 @@ class GQAAttention(Part):
         att = torch.empty_like(q)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
                             att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
-                            plan=ctx.attention_plan(self.window or 0, H, G) if xb.dtype == torch.bfloat16 else None)
+                            plan=plan)
         ops.gemm(att, self.w_o, residual, accumulate=True)
 
 

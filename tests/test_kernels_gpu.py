@@ -289,6 +289,15 @@ def test_gemm_tcgen05(m, n, k, accumulate):
     gemm_case("tc", m, n, k, accumulate)
 
 
+@pytest.mark.parametrize("m,n,k", [(64, 4096, 12288), (17, 4096, 4096), (33, 6144, 4096), (64, 1000, 1040), (128, 384, 8192)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_tcgen05_with_k_slices(m, n, k, accumulate):
+    # fewer output tiles than SMs: K is cut into slices whose partial sums are added in order
+    from hk_b200.csrc import gemm_fast
+    assert gemm_fast.tc_config(m, n, k, 148)[1] > 1
+    gemm_case("tc", m, n, k, accumulate)
+
+
 def test_gemm_tcgen05_many_tiles_per_cta():
     # more tiles than SMs x 2: every CTA walks several tiles through both accumulator buffers
     gemm_case("tc", 2048, 24576, 256, False)
@@ -318,7 +327,8 @@ def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
                        torch.zeros(65, 8, device=DEV))
 
 
-@pytest.mark.parametrize("m,f,k", [(128, 128, 64), (300, 384, 200), (2048, 1536, 512), (7, 256, 128), (64, 128, 64), (65, 128, 64)])
+@pytest.mark.parametrize("m,f,k", [(128, 128, 64), (300, 384, 200), (2048, 1536, 512), (7, 256, 128), (64, 128, 64), (65, 128, 64),
+                                   (40, 1024, 4096)])
 def test_gemm_swiglu_paired_layout(m, f, k):
     from hk_b200.csrc import gemm_fast
     g = torch.Generator().manual_seed(m + f + k)

@@ -45,7 +45,7 @@ def make_case(seed, H, G, hd, pt, lens, splits, window):
 def ordinary(case):
     from hk_b200.csrc import ops
     out = torch.empty_like(case["q"])
-    with ops.force(attention="flash"):
+    with ops.force(attention="flash_cp"):      # the same kernels as the entry point under test
         ops.paged_attention(case["q"], case["k"], case["v"], case["bt"], case["pos"], case["slot"], out, case["H"], case["G"],
                             case["hd"], case["pt"], case["window"], 1.0 / math.sqrt(case["hd"]), plan=case["plan"])
     return out
