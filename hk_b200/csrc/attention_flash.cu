@@ -66,7 +66,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD, int NW>
-__global__ void __launch_bounds__(NW * 32)
+__global__ void __launch_bounds__(NW * 32, 3)
 attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int table_stride, const Item* __restrict__ items,
                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G,
@@ -172,18 +172,32 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
         mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
       }
     }
-    // ---- mask, scale, running maximum
+    // ---- mask, scale, running maximum.  A tile that every row of this thread sees whole (the common case
+    // far below the diagonal) needs no per-element tests.
     float mt[2] = {-CUDART_INF_F, -CUDART_INF_F};
+    const int j_first = t * TILE_N, j_last = t * TILE_N + TILE_N - 1;
+    const bool whole = valid[0] && valid[1] && j_first >= max(max(lo[0], lo[1]), it.kv_lo) &&
+                       j_last <= min(min(pos[0], pos[1]), it.kv_hi - 1);
+    if (whole) {
 #pragma unroll
-    for (int n = 0; n < TILE_N / 8; ++n)
+      for (int n = 0; n < TILE_N / 8; ++n)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const int j = t * TILE_N + n * 8 + 2 * qt + (e & 1);
-        const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
-        s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
-        mt[i] = fmaxf(mt[i], s[n][e]);
-      }
+        for (int e = 0; e < 4; ++e) {
+          s[n][e] *= scale_log2;
+          mt[e >> 1] = fmaxf(mt[e >> 1], s[n][e]);
+        }
+    } else {
+#pragma unroll
+      for (int n = 0; n < TILE_N / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int j = t * TILE_N + n * 8 + 2 * qt + (e & 1);
+          const bool ok = valid[i] && j >= lo[i] && j <= pos[i] && j >= it.kv_lo && j < it.kv_hi;
+          s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
+          mt[i] = fmaxf(mt[i], s[n][e]);
+        }
+    }
     float corr[2], msafe[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {

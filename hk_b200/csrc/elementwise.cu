@@ -277,6 +277,86 @@ __global__ void qk_norm_rope_kv_write_kernel(
   for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(v[i]);
 }
 
+// The same for head sizes up to 128 that are a multiple of 4 (and a rotary width that is a multiple of 8):
+// a lane holds 4 consecutive dims, read with one 16-byte load; the rotation partner (dim + rot/2) sits
+// (rot/8) lanes away and comes by shuffle, so nothing goes through shared memory.
+#define QKV_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(QKV_WARPS * 32)
+qk_norm_rope_kv_write_vec_kernel(
+    const float* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_w,
+    const float* __restrict__ k_w, float eps, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
+    const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
+    T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
+    int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int heads_total = H + (write_kv ? 2 * G : 0);
+  const long long item = (long long)blockIdx.x * QKV_WARPS + wid;
+  if (item >= (long long)n * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int hh = (int)(item % heads_total);
+  const int d0 = lane * 4;
+  const bool active = d0 < hd;
+  const float* src = qkv + (size_t)t * (H + 2 * G) * hd + (size_t)hh * hd;
+  float4 v = active ? *reinterpret_cast<const float4*>(src + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);
+  const int pos = positions[t];
+  if (kind != 2) {
+    const float* w = kind == 0 ? q_w : k_w;
+    if (w) {
+      float ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+      if (active) {
+        const float4 g = *reinterpret_cast<const float4*>(w + d0);
+        v = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+      }
+    }
+    if (rot > 0) {
+      const int half = rot >> 1, shift = half >> 2;        // partner lanes are `shift` apart
+      const bool low = d0 < half, in_rot = d0 < rot;
+      const int partner = low ? lane + shift : lane - shift;
+      const int src_lane = in_rot ? partner : lane;
+      float4 p;
+      p.x = __shfl_sync(0xffffffffu, v.x, src_lane);
+      p.y = __shfl_sync(0xffffffffu, v.y, src_lane);
+      p.z = __shfl_sync(0xffffffffu, v.z, src_lane);
+      p.w = __shfl_sync(0xffffffffu, v.w, src_lane);
+      if (in_rot) {
+        const int i0 = low ? d0 : d0 - half;                // index into the tables
+        const float4 c = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + i0);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + i0);
+        // low half: x' = a c - b s (a = own, b = partner); high half: x' = a s + b c (a = partner, b = own)
+        if (low)
+          v = make_float4(v.x * c.x - p.x * sn.x, v.y * c.y - p.y * sn.y, v.z * c.z - p.z * sn.z, v.w * c.w - p.w * sn.w);
+        else
+          v = make_float4(p.x * sn.x + v.x * c.x, p.y * sn.y + v.y * c.y, p.z * sn.z + v.z * c.z, p.w * sn.w + v.w * c.w);
+      }
+    }
+  }
+  if (!active) return;
+  T* dst;
+  if (kind == 0) {
+    dst = q_out + (size_t)t * H * hd + (size_t)hh * hd;
+  } else {
+    const int g = kind == 1 ? hh - H : hh - H - G;
+    const int page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
+    if (page < 0) return;
+    T* base = kind == 1 ? k_pages : v_pages;
+    dst = base + (((size_t)page * G + g) * page_tokens + (pos % page_tokens)) * hd;
+  }
+  if (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + d0) = v;
+  } else {
+    __nv_bfloat162 lo2 = __floats2bfloat162_rn(v.x, v.y), hi2 = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(dst) + d0) =
+        make_uint2(*reinterpret_cast<uint32_t*>(&lo2), *reinterpret_cast<uint32_t*>(&hi2));
+  }
+}
+
 HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, const float* q_w,
                                     const float* k_w, float eps, const float* cos_t, const float* sin_t,
                                     int rot, const int* positions, const int* slot_of_token,
@@ -287,6 +367,20 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
   if (hd > QKR_MAX_HD || hd < 2 || rot > hd || (rot & 1)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   long long items = (long long)n * (H + (write_kv ? 2 * G : 0));
+  const bool aligned = ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_w |
+                          (uintptr_t)k_w | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0);
+  if (hd <= 128 && (hd & 3) == 0 && (rot & 7) == 0 && aligned) {
+    unsigned vblocks = (unsigned)((items + QKV_WARPS - 1) / QKV_WARPS);
+    if (dtype == HK_F32)
+      return hk_launch(qk_norm_rope_kv_write_vec_kernel<float>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (float*)q_out,
+                       q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
+                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv);
+    if (dtype == HK_BF16)
+      return hk_launch(qk_norm_rope_kv_write_vec_kernel<bf16>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
+                       k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
+                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv);
+    return HK_ERR_UNSUPPORTED;
+  }
   unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
   if (dtype == HK_F32)
     return hk_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (float*)q_out, q_w,
