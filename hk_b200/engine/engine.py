@@ -127,6 +127,12 @@ class Engine:
         limit = getattr(config, "max_position_embeddings", None) or max_tokens
         self.max_context = int(max_context) if max_context else int(min(limit, max_tokens))
         self.max_batch_tokens = int(max_batch_tokens)
+        # compile, side by side, the kernel libraries this precision runs on (and only those)
+        from ..csrc import build as _build
+        needed = ["elementwise", "gemm_generic", "attention_generic"]
+        if self.precision.compute == torch.bfloat16:
+            needed += ["gemm_smallm", "gemm_tc", "attention_flash"]
+        _build.build_many(needed)
         self.model = build_model(config, self.max_context)
         specs = self.model.param_specs()
         with torch.no_grad():

@@ -1,0 +1,114 @@
+"""Single-kernel cases with device timing: `python -m hk_b200.profiling <case> [sizes]`.
+
+Each case sets up one hot kernel of the engine at a serving size, runs it a few times, times it
+with CUDA events (L2 flushed between runs by writing a buffer larger than L2) and prints the
+achieved GB/s or TFLOP/s.  The same command under `ncu -k regex:<kernel>` gives the hardware
+counters for that kernel.  (The reference has per-kernel event timing of the same kind behind
+HK_CUDA_EVENTS: src/cuda.zig:1212-1263.)
+
+Cases: gemm_tc (tcgen05 product, --swiglu / --add), gemm_smallm (decode product), attn_decode
+(paged decode attention), attn_prefill (paged causal attention of one prompt).
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import numpy as np
+import torch
+
+
+def _time(fn, reps: int, flush: torch.Tensor):
+    times = []
+    for i in range(reps + 2):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(a.elapsed_time(b) * 1e3)
+    return float(np.median(times))
+
+
+def _paged(batch, ctx, G, hd, pt, dev):
+    pages_per = -(-ctx // pt)
+    n_pages = batch * pages_per
+    k = torch.randn(n_pages, G, pt, hd, device=dev).to(torch.bfloat16)
+    v = torch.randn(n_pages, G, pt, hd, device=dev).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, device=dev).to(torch.int32).view(batch, pages_per)
+    return k, v, perm.contiguous()
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="hk_b200.profiling")
+    ap.add_argument("case", choices=["gemm_tc", "gemm_smallm", "attn_decode", "attn_prefill"])
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--n", type=int, default=24576)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--add", action="store_true")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-tokens", type=int, default=16)
+    ap.add_argument("--reps", type=int, default=5)
+    a = ap.parse_args(argv)
+    from .csrc import attention_fast, gemm_fast, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    if a.case in ("gemm_tc", "gemm_smallm"):
+        x = (torch.randn(a.m, a.k, device=dev) / 8).to(torch.bfloat16)
+        w = (torch.randn(a.n, a.k, device=dev) / 8).to(torch.bfloat16)
+        if a.swiglu:
+            out = torch.empty(a.m, a.n // 2, dtype=torch.bfloat16, device=dev)
+            fn = lambda: ops.gemm_swiglu(x, w, out, gemm_fast.PAIR)
+        else:
+            out = torch.zeros(a.m, a.n, dtype=torch.float32, device=dev)
+            fn = lambda: ops.gemm(x, w, out, accumulate=a.add)
+        with ops.force(gemm="tc" if a.case == "gemm_tc" else "smallm"):
+            us = _time(fn, a.reps, flush)
+        flops = 2.0 * a.m * a.n * a.k
+        nbytes = 2.0 * (a.n * a.k + a.m * a.k) + out.numel() * out.element_size()
+        print(f"{a.case} M={a.m} N={a.n} K={a.k} swiglu={a.swiglu} add={a.add}: {us:.1f} us, "
+              f"{flops / us * 1e-6:.1f} TFLOP/s, {nbytes / us * 1e-3:.1f} GB/s")
+    else:
+        H, G, hd, pt = a.heads, a.kv_heads, a.head_dim, a.page_tokens
+        scale = 1.0 / math.sqrt(hd)
+        upload = lambda arr: torch.from_numpy(np.ascontiguousarray(arr)).to(dev)
+        if a.case == "attn_decode":
+            k, v, bt = _paged(a.batch, a.ctx, G, hd, pt, dev)
+            n = a.batch
+            q = torch.randn(n, H * hd, device=dev).to(torch.bfloat16)
+            pos = torch.full((n,), a.ctx - 1, dtype=torch.int32, device=dev)
+            slot = torch.arange(n, dtype=torch.int32, device=dev)
+            splits = max(1, min(32, 2 * sms // (n * G)))
+            plan = attention_fast.build_plan(list(range(n)), list(range(n)), [1] * n, [a.ctx - 1] * n, n, 0, H, G, sms, upload,
+                                             fixed_splits=splits)
+            nbytes = 2.0 * 2 * n * a.ctx * G * hd
+            flops = 4.0 * n * H * hd * a.ctx
+        else:
+            k, v, bt = _paged(1, a.ctx, G, hd, pt, dev)
+            n = a.ctx
+            q = torch.randn(n, H * hd, device=dev).to(torch.bfloat16)
+            pos = torch.arange(n, dtype=torch.int32, device=dev)
+            slot = torch.zeros(n, dtype=torch.int32, device=dev)
+            plan = attention_fast.build_plan([0], [0], [n], [0], n, 0, H, G, sms, upload)
+            nbytes = 2.0 * 2 * n * G * hd + 2 * 2.0 * n * H * hd
+            flops = 4.0 * H * hd * n * (n + 1) / 2
+        out = torch.empty_like(q)
+        fn = lambda: ops.paged_attention(q, k, v, bt, pos, slot, out, H, G, hd, pt, 0, scale, plan=plan)
+        us = _time(fn, a.reps, flush)
+        print(f"{a.case} batch={a.batch} ctx={a.ctx} H={H} G={G} hd={hd} page={pt}: {us:.1f} us, "
+              f"{flops / us * 1e-6:.1f} TFLOP/s, {nbytes / us * 1e-3:.1f} GB/s (cache bytes / time)")
+    gemm_fast.check_status(dev)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
