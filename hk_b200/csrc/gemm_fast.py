@@ -1,6 +1,6 @@
 """Choice among the bfloat16 tensor-core matrix products.
 
-  * up to 16 rows (small decode batches): the weight-streaming mma.sync kernel (`gemm_smallm.cu`);
+  * up to 8 rows (small decode batches): the weight-streaming mma.sync kernel (`gemm_smallm.cu`);
   * more rows (larger decode batches, prefill, mixed batches): the persistent tcgen05 kernel
     (`gemm_tc.cu`), cutting K into slices when the output has fewer tiles than the GPU has SMs.
 The choice depends on the shape alone.  Shapes both refuse (K not a multiple of 8, unaligned
@@ -17,7 +17,7 @@ from . import build
 
 _UNSUPPORTED = 100001
 SMALL_M = 64          # the most rows the weight-streaming kernel takes
-SMALL_M_AUTO = 16     # up to here it is chosen; above, the tcgen05 kernel with K slices streams better
+SMALL_M_AUTO = 8      # up to here it is chosen (measured); above, the tcgen05 kernel with K slices streams better
 _status = {}
 _sm_count = {}
 
@@ -69,9 +69,10 @@ def row_tiles(M: int, N: int, device) -> int:
 
 
 def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
-    """Tile width and number of K slices for the tcgen05 kernel.  Wide tiles when they still fill the SMs;
-    with fewer output tiles than SMs (few rows: decode batches, narrow outputs) K is cut into slices so that
-    every SM streams a share of the weights."""
+    """Tile width and number of K slices for the tcgen05 kernel.  Wide tiles when they still fill half
+    the SMs; with fewer output tiles than SMs (few rows: decode batches, narrow outputs) K is cut into
+    slices so that every SM streams a share of the weights.  (A finer cost model that also weighed wave
+    tails chose more slices and measured slower: the second kernel that adds the slices has a fixed cost.)"""
     m_tiles = -(-M // 128)
     if bn == 0:
         bn = 256 if N >= 256 and m_tiles * -(-N // 256) >= sms // 2 else 128
