@@ -30,7 +30,22 @@ TINY_C = dict(
     use_sliding_window=True, sliding_window=20,
     layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"])
 
-TINY = {"A": (TINY_A, 0, 0.02, 0.05), "B": (TINY_B, 1, 0.03, 0.1), "C": (TINY_C, 5, 0.05, 0.1)}
+# Two more with the head sizes of real checkpoints (64 and 128), which take the TMA-fed decode attention and
+# the widest flash tiles: D has 3 query heads per kv head and a window on its middle layer, E one kv head.
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=136, num_hidden_layers=3,
+    intermediate_size=264, num_attention_heads=6, num_key_value_heads=2, head_dim=64, vocab_size=777,
+    rope_theta=250000.0, rms_norm_eps=2e-6, tie_word_embeddings=True, max_position_embeddings=1024,
+    hidden_act="silu", attention_bias=False, initializer_range=0.04, use_sliding_window=True, sliding_window=70,
+    layer_types=["full_attention", "sliding_attention", "full_attention"])
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=256, num_hidden_layers=2,
+    intermediate_size=384, num_attention_heads=4, num_key_value_heads=1, head_dim=128, vocab_size=1000,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048,
+    hidden_act="silu", attention_bias=False, initializer_range=0.03)
+
+TINY = {"A": (TINY_A, 0, 0.02, 0.05), "B": (TINY_B, 1, 0.03, 0.1), "C": (TINY_C, 5, 0.05, 0.1),
+        "D": (TINY_D, 6, 0.04, 0.1), "E": (TINY_E, 7, 0.03, 0.05)}
 
 _ST_DTYPES = {"F32": np.float32, "F16": np.float16, "F64": np.float64, "I32": np.int32, "I64": np.int64}
 
