@@ -57,15 +57,13 @@ def _aligned(a, w) -> bool:
     return a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
+_rt_override = 0      # tests and tuning runs may pin the row tiles per CTA
+
+
 def row_tiles(M: int, N: int, device) -> int:
-    """Row tiles of 16 per CTA for the small-M kernel: as fat as the grid allows while it still
-    fills the SMs twice over (fat CTAs read the activations from L2 less often)."""
-    sms = _sms(device)
-    limit = 4 if M <= 16 else 2
-    rt = limit
-    while rt > 1 and -(-N // (16 * rt)) < 2 * sms:
-        rt //= 2
-    return rt
+    """Row tiles of 16 per CTA for the small-M kernel.  One: measured fastest at every decode shape of the
+    8B model (more, smaller CTAs per SM hide the latency of the weight loads better than fat ones)."""
+    return _rt_override or 1
 
 
 def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):

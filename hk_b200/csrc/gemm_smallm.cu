@@ -65,8 +65,9 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
 #pragma unroll
   for (int j = 0; j < MT; ++j) arow[j] = a + (size_t)min(j * 8 + g, M - 1) * K;
 
-  uint4 wf[RT][2][2];   // [row tile][row g / g+8][k half of the chunk]
-  auto load_w = [&](int c) {
+  // Two chunks of weights are always on their way while a third is multiplied.
+  uint4 wf[2][RT][2][2];   // [buffer][row tile][row g / g+8][k half of the chunk]
+  auto load_w = [&](int c, int b) {
     const int k0 = c * KCHUNK + t * 8;
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -75,23 +76,10 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
 #pragma unroll
         for (int kh = 0; kh < 2; ++kh) {
           const int k = k0 + kh * 32;
-          wf[r][h][kh] = k < K ? ldg_stream(wrow[r][h] + k) : make_uint4(0, 0, 0, 0);
+          wf[b][r][h][kh] = k < K ? ldg_stream(wrow[r][h] + k) : make_uint4(0, 0, 0, 0);
         }
   };
-
-  // The weights do not depend on the kernel before: the first chunk is on its way before this kernel waits
-  // for that kernel's output (the activations).
-  if (c_begin < c_end) load_w(c_begin);
-  pdl_wait();
-  for (int c = c_begin; c < c_end; ++c) {
-    uint4 cur[RT][2][2];
-#pragma unroll
-    for (int r = 0; r < RT; ++r)
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int kh = 0; kh < 2; ++kh) cur[r][h][kh] = wf[r][h][kh];
-    if (c + 1 < c_end) load_w(c + 1);   // the next chunk's loads fly while this one is multiplied
+  auto multiply = [&](int c, uint4 (&cur)[RT][2][2]) {
     const int k0 = c * KCHUNK + t * 8;
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
@@ -108,6 +96,33 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
           mma_bf16_16816(acc[r][j], a1, x.z, x.w);
         }
       }
+    }
+  };
+
+  // The weights do not depend on the kernel before: the first chunks are on their way before this kernel
+  // waits for that kernel's output (the activations).
+  if (c_begin < c_end) load_w(c_begin, 0);
+  if (c_begin + 1 < c_end) load_w(c_begin + 1, 1);
+  pdl_wait();
+  for (int c = c_begin; c < c_end; c += 2) {
+    uint4 cur[RT][2][2];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) cur[r][h][kh] = wf[0][r][h][kh];
+    if (c + 2 < c_end) load_w(c + 2, 0);
+    multiply(c, cur);
+    if (c + 1 < c_end) {
+#pragma unroll
+      for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int kh = 0; kh < 2; ++kh) cur[r][h][kh] = wf[1][r][h][kh];
+      if (c + 3 < c_end) load_w(c + 3, 1);
+      multiply(c + 1, cur);
     }
   }
 
