@@ -41,14 +41,20 @@ def supported(hd: int, group: int) -> bool:
     return hd % 16 == 0 and 16 <= hd <= MAX_HD and group <= 64
 
 
+def tc_prefill_supported(hd: int, group: int) -> bool:
+    return hd in (64, 128) and group <= 128
+
+
 def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
                sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0,
-               max_context: int = 0) -> Optional[FlashPlan]:
+               max_context: int = 0, prefill_rows: int = 64) -> Optional[FlashPlan]:
     """`upload(int32 array) -> device tensor`.  `fixed_splits` > 0 forces that many items per run
     (a shape that does not change from step to step, for captured decode graphs); `max_context`
-    then bounds the key range any later step can bring, which sizes the kernel's page-id buffer."""
+    then bounds the key range any later step can bring, which sizes the kernel's page-id buffer.
+    `prefill_rows`: rows per CTA for batches with prompt portions: 64 (the mma.sync kernel) or 128 (the
+    tcgen05 kernel, head sizes 64 and 128)."""
     group = H // G
-    nw = 1 if all(l == 1 for l in q_lens) else 4
+    nw = 1 if all(l == 1 for l in q_lens) else prefill_rows // 16
     rows = 16 * nw
     if group > rows:
         if group > 64:
@@ -63,6 +69,9 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
             kv_hi = pos0 + n
             kv_lo = max(0, pos0 - window + 1) if window > 0 else 0
             runs.append((qs + b0, n, slot, pos0, kv_lo, kv_hi))
+    if nw != 1:
+        # longest key ranges first: the heavy items of a causal prompt (its last rows) must not form the tail
+        runs.sort(key=lambda r: r[4] - r[5])
     base_ctas = len(runs) * G
     items = np.zeros((0, 8), dtype=np.int32)
     recs = []
@@ -74,7 +83,7 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
         kv_len = kv_hi - kv_lo
         if fixed_splits > 0:
             want = fixed_splits
-        elif base_ctas >= 2 * sm_count:
+        elif base_ctas >= 2 * sm_count or nw == 8:
             want = 1
         else:
             want = max(1, min(2 * sm_count // base_ctas, kv_len // 64, 32))
@@ -123,6 +132,18 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
     if plan.n_parts:
         part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
+    if plan.nw == 8:
+        if plan.n_parts or not tc_prefill_supported(hd, H // G):
+            return False
+        lib_tc = build.load("attention_prefill_tc")
+        code = lib_tc.hk_attention_prefill_tc(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]), _ptr(plan.items),
+            plan.n_items, _ptr(out), H, G, hd, int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
+            plan.max_keys // int(page_tokens) + 2, _ptr(gemm_fast.status_flag(q.device)), stream)
+        if code == _UNSUPPORTED:
+            return False
+        ops._check(code, "paged_attention (tcgen05 prefill)")
+        return True
     code = _UNSUPPORTED
     if plan.nw == 1 and allow_tma and tma_decode_supported(hd, H // G, int(page_tokens)):
         code = lib.hk_attention_decode_tma(

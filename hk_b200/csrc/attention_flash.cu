@@ -127,18 +127,23 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   auto load_tile = [&](int t, int stage) {
     bf16* kd = ks + stage * TILE_N * LD;
     bf16* vd = vs + stage * TILE_N * LD;
-    int* pg = tile_pages + stage * TILE_N;
+    int* pg = tile_pages + stage * TILE_N;     // per key row: its row in the [rows, HD] view of the pages, or -1
     for (int r = threadIdx.x; r < TILE_N; r += NW * 32) {
       const int j = t * TILE_N + r;
-      pg[r] = (j >= it.kv_lo && j < it.kv_hi) ? bt[j / page_tokens] : -1;
+      int row_of_key = -1;
+      if (j >= it.kv_lo && j < it.kv_hi) {
+        const int pi = j / page_tokens;
+        const int page = bt[pi];
+        if (page >= 0) row_of_key = (page * G + g) * page_tokens + (j - pi * page_tokens);
+      }
+      pg[r] = row_of_key;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < TILE_N * CPR; idx += NW * 32) {
       const int r = idx / CPR, c = idx % CPR;
-      const int j = t * TILE_N + r;
-      const int page = pg[r];
-      const bool ok = page >= 0;
-      const size_t off = ok ? (((size_t)page * G + g) * page_tokens + (j % page_tokens)) * HD + c * 8 : 0;
+      const int row_of_key = pg[r];
+      const bool ok = row_of_key >= 0;
+      const size_t off = ok ? (size_t)row_of_key * HD + c * 8 : 0;
       cp_async16(kd + r * LD + c * 8, k_pages + off, ok);
       cp_async16(vd + r * LD + c * 8, v_pages + off, ok);
     }

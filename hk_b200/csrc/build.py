@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_tc": "gemm_tc.cu",
     "gemm_smallm": "gemm_smallm.cu",
     "attention_flash": "attention_flash.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
 }
 HEADERS: List[str] = ["common.cuh", "attention_noalloc.h"]
 
@@ -81,12 +82,17 @@ def build_dir() -> str:
         return d
 
 
+def _extra_flags() -> List[str]:
+    """Extra nvcc flags from HK_B200_NVCC_FLAGS (for instance -DHK_TRACE); they are part of a built file's name."""
+    return os.environ.get("HK_B200_NVCC_FLAGS", "").split()
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     for fn in [LIBRARIES[name]] + HEADERS:
         with open(os.path.join(HERE, fn), "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -108,7 +114,7 @@ def build(name: str, verbose: bool = True) -> str:
     nvcc = find_nvcc()
     src = os.path.join(HERE, LIBRARIES[name])
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", HERE, "-o", tmp, src]
+    cmd = [nvcc] + NVCC_FLAGS + _extra_flags() + ["-I", HERE, "-o", tmp, src]
     if verbose:
         _say(f"compiling {LIBRARIES[name]} for sm_100a ...")
     t0 = time.time()

@@ -31,12 +31,12 @@ class StepContext:
     plans: Dict[tuple, object] = field(default_factory=dict)
     plan_builder: Optional[object] = None
 
-    def attention_plan(self, window: int, n_heads: int, n_kv_heads: int):
-        """The cut of this batch into work items for the flash attention kernel, built once per
-        step and (window, heads, groups); None sends attention to the generic kernel."""
+    def attention_plan(self, window: int, n_heads: int, n_kv_heads: int, head_dim: int):
+        """The cut of this batch into work items for the flash attention kernels, built once per step
+        and (window, heads, groups, head size); None sends attention to the generic kernel."""
         if self.plan_builder is None:
             return None
-        key = (window, n_heads, n_kv_heads)
+        key = (window, n_heads, n_kv_heads, head_dim)
         if key not in self.plans:
-            self.plans[key] = self.plan_builder(self, window, n_heads, n_kv_heads)
+            self.plans[key] = self.plan_builder(self, window, n_heads, n_kv_heads, head_dim)
         return self.plans[key]

@@ -131,7 +131,7 @@ class Engine:
         from ..csrc import build as _build
         needed = ["elementwise", "gemm_generic", "attention_generic"]
         if self.precision.compute == torch.bfloat16:
-            needed += ["gemm_smallm", "gemm_tc", "attention_flash"]
+            needed += ["gemm_smallm", "gemm_tc", "attention_flash", "attention_prefill_tc"]
         _build.build_many(needed)
         self.model = build_model(config, self.max_context)
         specs = self.model.param_specs()
@@ -182,11 +182,12 @@ class Engine:
     def free_pages(self) -> List[int]:
         return self.cache.books.free_pages()
 
-    def _flash_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int):
-        from ..csrc import attention_fast
+    def _flash_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int, head_dim: int):
+        from ..csrc import attention_fast, ops
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        tc = attention_fast.tc_prefill_supported(head_dim, n_heads // n_kv_heads) and ops._forced["attention"] != "flash_cp"
         return attention_fast.build_plan(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens, window,
-                                         n_heads, n_kv_heads, sms, self.stager.upload)
+                                         n_heads, n_kv_heads, sms, self.stager.upload, prefill_rows=128 if tc else 64)
 
     # -- the step function -------------------------------------------------------------------
     def check_step(self, entries: Sequence[StepEntry]) -> None:

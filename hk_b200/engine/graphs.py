@@ -43,9 +43,9 @@ class DecodeGraph:
         # follows; at most 32 splits (the reference stops at 16: src/cuda/engine.zig:96-101)
         return max(1, min(32, 2 * self.sms // (self.batch * n_kv_heads)))
 
-    def _build_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int):
+    def _build_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int, head_dim: int):
         from ..csrc import attention_fast
-        key = (window, n_heads, n_kv_heads)
+        key = (window, n_heads, n_kv_heads, head_dim)
         bufs = self.plan_buffers.setdefault(key, [])
         idx = [0]
 

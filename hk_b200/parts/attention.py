@@ -81,7 +81,7 @@ class GQAAttention(Part):
         H, G, hd = self.H, self.G, self.hd
         # the attention work items are uploaded before any kernel of this layer is launched (kernels may start
         # ahead of their predecessor and read such host-written tables early)
-        plan = ctx.attention_plan(self.window or 0, H, G) if xb.dtype == torch.bfloat16 else None
+        plan = ctx.attention_plan(self.window or 0, H, G, hd) if xb.dtype == torch.bfloat16 else None
         qkv = torch.empty((n, (H + 2 * G) * hd), dtype=torch.float32, device=xb.device)
         ops.gemm(xb, self.w_qkv, qkv)
         q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)

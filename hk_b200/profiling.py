@@ -56,6 +56,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--mma", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--row-tiles", type=int, default=0, help="gemm_smallm: pin the row tiles of 16 per CTA (1, 2 or 4)")
     a = ap.parse_args(argv)
     from .csrc import attention_fast, gemm_fast, ops
@@ -100,7 +101,8 @@ def main(argv=None) -> int:
             q = torch.randn(n, H * hd, device=dev).to(torch.bfloat16)
             pos = torch.arange(n, dtype=torch.int32, device=dev)
             slot = torch.zeros(n, dtype=torch.int32, device=dev)
-            plan = attention_fast.build_plan([0], [0], [n], [0], n, 0, H, G, sms, upload)
+            plan = attention_fast.build_plan([0], [0], [n], [0], n, 0, H, G, sms, upload,
+                                             prefill_rows=128 if attention_fast.tc_prefill_supported(hd, H // G) and not a.mma else 64)
             nbytes = 2.0 * 2 * n * G * hd + 2 * 2.0 * n * H * hd
             flops = 4.0 * H * hd * n * (n + 1) / 2
         out = torch.empty_like(q)

@@ -204,7 +204,8 @@ def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=Non
             q_starts.append(q_starts[-1] + c)
         plan = attention_fast.build_plan(list(range(len(lens))), q_starts, [c for _, c in q_spans], [p0 for p0, _ in q_spans],
                                          n, window, H, G, sm_count, lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV),
-                                         fixed_splits=fixed_splits)
+                                         fixed_splits=fixed_splits,
+                                         prefill_rows=128 if kernel == "flash" and attention_fast.tc_prefill_supported(hd, H // G) else 64)
     with ops().force(attention=kernel):
         ops().paged_attention(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), bt.to(DEV), pos_t.to(DEV), slot_t.to(DEV), out,
                               H, G, hd, pt, window, scale, plan=plan)
@@ -358,13 +359,28 @@ FLASH_SHAPES = [(4, 2, 16, 4), (5, 1, 48, 16), (6, 2, 80, 8), (8, 2, 128, 16), (
                 (32, 8, 128, 16), (12, 4, 96, 64), (40, 2, 64, 16)]
 
 
+@pytest.mark.parametrize("kernel", ["flash", "flash_cp"])
 @pytest.mark.parametrize("H,G,hd,pt", FLASH_SHAPES)
 @pytest.mark.parametrize("window", [0, 13, 100])
-def test_attention_flash_mixed_batch(H, G, hd, pt, window):
-    # a decode token deep in a long request, a portion that starts off-tile, a fresh request, a two-token portion
-    out, want, _ = attention_case("flash", torch.bfloat16, H, G, hd, pt, window, [300, 170, 5, 131],
+def test_attention_flash_mixed_batch(kernel, H, G, hd, pt, window):
+    # a decode token deep in a long request, a portion that starts off-tile, a fresh request, a two-token portion.
+    # 'flash' takes the tcgen05 kernel for head sizes 64 and 128, 'flash_cp' always the mma.sync one.
+    out, want, _ = attention_case(kernel, torch.bfloat16, H, G, hd, pt, window, [300, 170, 5, 131],
                                   [(299, 1), (37, 133), (0, 5), (129, 2)])
     close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    from hk_b200.csrc import gemm_fast
+    gemm_fast.check_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("H,G,hd,pt,window", [(32, 8, 128, 16, 0), (8, 2, 64, 16, 0), (6, 2, 128, 32, 200), (5, 1, 64, 16, 0),
+                                              (16, 1, 128, 16, 0), (3, 3, 128, 8, 0)])
+def test_attention_tcgen05_prefill_long_prompt(H, G, hd, pt, window):
+    # several 128-key tiles per CTA and several CTAs per request: a 700-token prompt whole, and a portion that starts
+    # at position 391 of another request
+    out, want, _ = attention_case("flash", torch.bfloat16, H, G, hd, pt, window, [700, 650], [(0, 700), (391, 259)])
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    from hk_b200.csrc import gemm_fast
+    gemm_fast.check_status(torch.device(DEV))
 
 
 @pytest.mark.parametrize("kernel", ["flash", "flash_cp"])
