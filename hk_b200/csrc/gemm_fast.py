@@ -66,6 +66,16 @@ def row_tiles(M: int, N: int, device) -> int:
     return _rt_override or 1
 
 
+_cs_override = 0
+
+
+def cluster_size(M: int, N: int, rt: int, device) -> int:
+    """CTAs per cluster that split K for one tile of 16 rows in the small-M kernel.  One: splitting K over a
+    cluster (partial sums through distributed shared memory) measured slower at every decode shape of the 8B
+    model, narrow outputs included - the cluster launch and its barrier cost more than the idle SMs."""
+    return _cs_override or 1
+
+
 def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
     """Tile width and number of K slices for the tcgen05 kernel.  Wide tiles when they still fill half
     the SMs; with fewer output tiles than SMs (few rows: decode batches, narrow outputs) K is cut into
@@ -93,8 +103,9 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
         if M > SMALL_M:
             return False
         lib = build.load("gemm_smallm")
+        rt = row_tiles(M, N, a.device)
         code = lib.hk_gemm_smallm(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(N), 1 if accumulate else 0,
-                                  row_tiles(M, N, a.device), _stream())
+                                  rt, cluster_size(M, N, rt, a.device), _stream())
         if code == _UNSUPPORTED:
             return False
         ops._check(code, "gemm (small-M)")

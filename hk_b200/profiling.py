@@ -56,11 +56,13 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--cluster", type=int, default=0, help="gemm_smallm: pin the CTAs per cluster that split K (1, 2 or 4)")
     ap.add_argument("--mma", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--row-tiles", type=int, default=0, help="gemm_smallm: pin the row tiles of 16 per CTA (1, 2 or 4)")
     a = ap.parse_args(argv)
     from .csrc import attention_fast, gemm_fast, ops
     gemm_fast._rt_override = a.row_tiles
+    gemm_fast._cs_override = a.cluster
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2

@@ -312,6 +312,19 @@ def test_gemm_small_m(m, n, k):
     gemm_case("smallm", m, n, k, True, seed=1)
 
 
+@pytest.mark.parametrize("cs", [2, 4])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 300, 1032), (16, 64, 8192)])
+def test_gemm_small_m_cluster_split_k(cs, m, n, k):
+    # K split over a thread-block cluster, partial sums through distributed shared memory
+    from hk_b200.csrc import gemm_fast
+    gemm_fast._cs_override = cs
+    try:
+        gemm_case("smallm", m, n, k, False)
+        gemm_case("smallm", m, n, k, True, seed=2)
+    finally:
+        gemm_fast._cs_override = 0
+
+
 def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
     a = torch.randn(4, 70).to(torch.bfloat16).to(DEV)      # K % 8 != 0
     w = torch.randn(9, 70).to(torch.bfloat16).to(DEV)
