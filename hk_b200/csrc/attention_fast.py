@@ -61,6 +61,8 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
             return None
         nw, rows = 4, 64
     tpb = rows // group
+    if fixed_splits > 0 and nw == 1:
+        return _decode_plan(slots, q_starts, start_positions, n_tokens, window, fixed_splits, max_context, upload)
     runs = []
     for slot, qs, ql, p0 in zip(slots, q_starts, q_lens, start_positions):
         for b0 in range(0, ql, tpb):
@@ -109,6 +111,43 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
     if n_parts:
         meta = upload(np.stack([first, count, row0]))
         plan.first, plan.count, plan.row0 = meta[0], meta[1], meta[2]
+    return plan
+
+
+def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max_context, upload) -> FlashPlan:
+    """The plan of a batch of single tokens with a fixed number of key splits, in array arithmetic (this runs
+    on the host before every replayed decode step).  Same items as the general loop gives."""
+    B = len(slots)
+    pos = np.asarray(start_positions, dtype=np.int64)
+    slot = np.asarray(slots, dtype=np.int64)
+    qrow = np.asarray(q_starts, dtype=np.int64)
+    kv_hi = pos + 1
+    kv_lo = np.maximum(0, pos - window + 1) if window > 0 else np.zeros(B, dtype=np.int64)
+    kv_len = kv_hi - kv_lo
+    max_keys = int(kv_len.max()) if B else 0
+    if max_context > 0:
+        max_keys = max(max_keys, -(-max_context // splits) + 2 * TILE_N)
+    items = np.zeros((B, splits, 8), dtype=np.int32)
+    items[:, :, 0] = qrow[:, None]
+    items[:, :, 1] = 1
+    items[:, :, 2] = slot[:, None]
+    items[:, :, 3] = pos[:, None]
+    if splits == 1:
+        items[:, 0, 4], items[:, 0, 5], items[:, 0, 6] = kv_lo, kv_hi, -1
+        return FlashPlan(1, B, upload(items.reshape(B, 8)), 0, max_keys)
+    chunk = -(-(-(-kv_len // splits)) // TILE_N) * TILE_N
+    start = (kv_lo // TILE_N) * TILE_N
+    s = np.arange(splits, dtype=np.int64)[None, :]
+    a = np.maximum(kv_lo[:, None], start[:, None] + s * chunk[:, None])
+    b = np.maximum(a, np.minimum(kv_hi[:, None], start[:, None] + (s + 1) * chunk[:, None]))
+    items[:, :, 4], items[:, :, 5] = a, b
+    items[:, :, 6] = np.arange(B, dtype=np.int64)[:, None] * splits + s
+    meta = np.zeros((3, n_tokens), dtype=np.int32)
+    meta[0, qrow] = np.arange(B) * splits
+    meta[1, qrow] = splits
+    plan = FlashPlan(1, B * splits, upload(items.reshape(B * splits, 8)), B * splits, max_keys)
+    m = upload(meta)
+    plan.first, plan.count, plan.row0 = m[0], m[1], m[2]
     return plan
 
 

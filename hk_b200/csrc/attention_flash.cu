@@ -778,7 +778,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 }
 
 // One warp per (token, head): merges `count[t]` partials starting at `first[t]` (row `row0[t] + head % group`).
-// Tokens with count 0 were written directly by the main kernel.
+// Tokens with count 0 were written directly by the main kernel.  The partials' (max, sum) pairs are read by
+// one lane each, the weights come from a warp-wide maximum, and the value rows are then added in partial
+// order with several loads in flight.
 template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          const int* __restrict__ first, const int* __restrict__ count,
@@ -794,27 +796,45 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   if (n <= 0) return;
   const int group = H / G, g = h / group;
   const int r = row0[t] + h % group;
+  const size_t base0 = ((size_t)first[t] * G + g) * rows + r;       // partial s sits at base0 + s * G * rows
+  const size_t step = (size_t)G * rows;
+  constexpr int PER = (HD + 31) / 32;
+  float acc[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
   float mm = -CUDART_INF_F;
-  for (int s = 0; s < n; ++s) mm = fmaxf(mm, part_ml[(((size_t)(first[t] + s) * G + g) * rows + r) * 2]);
-  float acc[(HD + 31) / 32];
-#pragma unroll
-  for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+  for (int s0 = 0; s0 < n; s0 += 32) {                               // the maximum over all partials
+    const int s = s0 + lane;
+    mm = fmaxf(mm, s < n ? part_ml[(base0 + s * step) * 2] : -CUDART_INF_F);
+  }
+  mm = warp_max(mm);
   float lsum = 0.f;
-  for (int s = 0; s < n; ++s) {
-    const size_t base = ((size_t)(first[t] + s) * G + g) * rows + r;
-    const float ms = part_ml[base * 2], ls = part_ml[base * 2 + 1];
-    const float f = ms == -CUDART_INF_F ? 0.f : exp2f(ms - mm);
-    lsum += ls * f;
+  for (int s0 = 0; s0 < n; s0 += 32) {
+    const int s = s0 + lane;
+    float f = 0.f, ls = 0.f;
+    if (s < n) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base0 + s * step) * 2);
+      f = ml.x == -CUDART_INF_F ? 0.f : exp2f(ml.x - mm);
+      ls = ml.y * f;
+    }
+    lsum += ls;                                                      // summed over the lanes below, in a fixed order
+    const int cnt = min(32, n - s0);
+#pragma unroll 8
+    for (int j = 0; j < cnt; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, f, j);
+      const float* po = part_o + (base0 + (size_t)(s0 + j) * step) * HD;
 #pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < HD) acc[i] += part_o[base * HD + d] * f;
+      for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        if (d < HD) acc[i] = fmaf(po[d], fj, acc[i]);
+      }
     }
   }
+  lsum = warp_sum(lsum);
   const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
   bf16* op = out + ((size_t)t * H + h) * HD;
 #pragma unroll
-  for (int i = 0; i < (HD + 31) / 32; ++i) {
+  for (int i = 0; i < PER; ++i) {
     const int d = lane + 32 * i;
     if (d < HD) op[d] = __float2bfloat16_rn(acc[i] * inv);
   }

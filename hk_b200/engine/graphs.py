@@ -26,40 +26,50 @@ class DecodeGraph:
         self.engine = engine
         self.batch = batch
         dev = engine.device
-        self.meta = torch.zeros((3, batch), dtype=torch.int32, device=dev)
+        # One static int32 buffer holds everything a step brings: token ids, positions and slots first, then
+        # each attention plan's arrays in the order the plans are built.  A replayed step fills a host copy of
+        # it and uploads it with ONE copy.
+        self.capacity = 3 * batch + 4 * (16 * batch * 8 + 3 * batch)
+        self.static = torch.zeros(self.capacity, dtype=torch.int32, device=dev)
+        self.meta = self.static[:3 * batch].view(3, batch)
         self.rows = torch.arange(batch, dtype=torch.int32, device=dev)
-        self.plan_buffers: Dict[tuple, List[torch.Tensor]] = {}
         self.plan_keys: List[tuple] = []
+        self.layout: List[tuple] = []        # (offset, size) of every array after the meta, as captured
         self.graph = None
         self.kernels = 0
         self.logits = None
-        self.ctx = None
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        self.sms = sms
+        self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self._pending: List[np.ndarray] = []
+        self._cursor = 0
+        self._immediate = True
 
-    # -- attention plans over static buffers ---------------------------------------------------
+    # -- attention plans over the static buffer --------------------------------------------------
     def _splits(self, n_kv_heads: int) -> int:
         # as many CTAs as are resident at once (two per SM), rounded down so that no second, thin wave
-        # follows; at most 32 splits (the reference stops at 16: src/cuda/engine.zig:96-101)
-        return max(1, min(32, 2 * self.sms // (self.batch * n_kv_heads)))
+        # follows; at most 16 splits, as in the reference (src/cuda/engine.zig:96-101): beyond that the merge of the
+        # partials costs more than the split saves
+        return max(1, min(16, 2 * self.sms // (self.batch * n_kv_heads)))
+
+    def _upload(self, arr: np.ndarray) -> torch.Tensor:
+        """The static region for `arr` (handed out in call order).  While capturing, the values are copied at
+        once; on replays they are collected and go up in one copy before the graph is launched."""
+        n = arr.size
+        off = self._cursor
+        if off + n > self.capacity:
+            raise RuntimeError("the decode graph's static buffer is too small for this model's attention plans")
+        self._cursor = off + n
+        region = self.static[off:off + n]
+        if self._immediate:
+            region.copy_(self.engine.stager.upload(arr).reshape(-1))
+            self.layout.append((off, n))
+        else:
+            self._pending.append(arr.reshape(-1))
+        return region.view(arr.shape)
 
     def _build_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int, head_dim: int):
         from ..csrc import attention_fast
-        key = (window, n_heads, n_kv_heads, head_dim)
-        bufs = self.plan_buffers.setdefault(key, [])
-        idx = [0]
-
-        def upload(arr: np.ndarray) -> torch.Tensor:
-            i = idx[0]
-            idx[0] += 1
-            src = self.engine.stager.upload(arr)
-            if i == len(bufs):
-                bufs.append(torch.empty_like(src))
-            bufs[i].copy_(src)
-            return bufs[i]
-
         return attention_fast.build_plan(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens, window,
-                                         n_heads, n_kv_heads, self.sms, upload, fixed_splits=self._splits(n_kv_heads),
+                                         n_heads, n_kv_heads, self.sms, self._upload, fixed_splits=self._splits(n_kv_heads),
                                          max_context=self.engine.max_context)
 
     def _context(self, slots, starts) -> StepContext:
@@ -73,9 +83,11 @@ class DecodeGraph:
     def run(self, meta: np.ndarray, slots, starts) -> torch.Tensor:
         """meta: int32 [3, B] (token ids, positions, slots).  Returns the logits [B, vocab]."""
         eng = self.engine
-        self.meta.copy_(eng.stager.upload(meta))
         ctx = self._context(slots, starts)
+        self._cursor = 3 * self.batch
         if self.graph is None:
+            self._immediate = True
+            self.meta.copy_(eng.stager.upload(meta))
             # an eager pass first: loads libraries, sets kernel attributes, builds the plans (whose
             # uploads must not be captured); it recomputes this very step, so the cache ends up the same
             x = eng.model.forward(ctx, eng.cache.layers)
@@ -90,10 +102,15 @@ class DecodeGraph:
             self.kernels = ops.launch_count() - before      # kernel nodes of the graph
             ops.count_launches(-self.kernels)               # capturing launched nothing
             self.graph = graph
-            self.ctx = ctx
+            self._immediate = False
         else:
+            self._pending = [meta.reshape(-1)]
             for key in self.plan_keys:
-                ctx.attention_plan(*key)      # refills the static buffers for this step
+                ctx.attention_plan(*key)      # collects this step's plan arrays, in the captured order
+            host = np.concatenate(self._pending)
+            if self._cursor != 3 * self.batch + sum(n for _, n in self.layout):
+                raise RuntimeError("a decode step's attention plans do not have the captured shape")
+            self.static[:host.size].copy_(eng.stager.upload(host))
         self.graph.replay()
         ops.count_launches(self.kernels)
         return self.logits.clone()      # the static buffer is overwritten by the next replay

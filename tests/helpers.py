@@ -44,8 +44,16 @@ TINY_E = dict(
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048,
     hidden_act="silu", attention_bias=False, initializer_range=0.03)
 
+# F is built to miss every fast path: a width that is no multiple of 8 (the tensor-core products need that),
+# plain multi-head attention (as many kv heads as heads) with the largest head size, an odd vocabulary.
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=100, num_hidden_layers=2,
+    intermediate_size=148, num_attention_heads=3, num_key_value_heads=3, head_dim=256, vocab_size=1001,
+    rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=300,
+    hidden_act="silu", attention_bias=False, initializer_range=0.02, partial_rotary_factor=0.25)
+
 TINY = {"A": (TINY_A, 0, 0.02, 0.05), "B": (TINY_B, 1, 0.03, 0.1), "C": (TINY_C, 5, 0.05, 0.1),
-        "D": (TINY_D, 6, 0.04, 0.1), "E": (TINY_E, 7, 0.03, 0.05)}
+        "D": (TINY_D, 6, 0.04, 0.1), "E": (TINY_E, 7, 0.03, 0.05), "F": (TINY_F, 8, 0.02, 0.05)}
 
 _ST_DTYPES = {"F32": np.float32, "F16": np.float16, "F64": np.float64, "I32": np.int32, "I64": np.int64}
 

@@ -33,6 +33,7 @@ CASES = {
     "C": dict(lengths=[40, 90, 130, 61, 77], page_tokens=16),
     "D": dict(lengths=[150, 37, 260, 90], page_tokens=16),
     "E": dict(lengths=[200, 75, 140], page_tokens=32),
+    "F": dict(lengths=[3, 50, 121], page_tokens=16),
 }
 
 _cache = {}
@@ -82,7 +83,7 @@ def families(seqs):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed", "mixed_tight"])
 def test_replay_matches_plain(tmp_path_factory, which, dtype, family):
     from hk_b200.engine import Engine
