@@ -81,6 +81,11 @@ def _check(code: int, what: str, launches: int = 1) -> None:
 _forced = {"gemm": None, "attention": None}
 
 
+def forced(kind: str) -> Optional[str]:
+    """The kernel family pinned for `kind` ('gemm' or 'attention'), or None."""
+    return _forced[kind]
+
+
 @contextlib.contextmanager
 def force(gemm: Optional[str] = None, attention: Optional[str] = None):
     """Pins the kernel family inside the block: gemm in {'generic','tc','smallm'},

@@ -1,5 +1,5 @@
 from .context import StepContext
-from .engine import (BatchTooLarge, Engine, EngineError, StepEntry, TokenOutOfRange, UnknownRequest, parse_dtype)
+from .engine import (BatchTooLarge, DeviceToken, Engine, EngineError, KernelTimeout, StepEntry, TokenOutOfRange, UnknownRequest, parse_dtype)
 
-__all__ = ["BatchTooLarge", "Engine", "EngineError", "StepContext", "StepEntry", "TokenOutOfRange",
+__all__ = ["BatchTooLarge", "DeviceToken", "Engine", "EngineError", "KernelTimeout", "StepContext", "StepEntry", "TokenOutOfRange",
            "UnknownRequest", "parse_dtype"]

@@ -43,12 +43,28 @@ class UnknownRequest(EngineError):
     pass
 
 
+class KernelTimeout(EngineError):
+    pass
+
+
+@dataclass
+class DeviceToken:
+    """One token id that is still on the device: element `index` of an int32 tensor (a sampler's
+    output that the host has not read yet).  It lets the next decode step be launched before the
+    host knows the token."""
+    tensor: torch.Tensor
+    index: int
+
+    def __len__(self) -> int:
+        return 1
+
+
 @dataclass
 class StepEntry:
     """A request's share of a step: its next tokens and the places among them (indices into
-    `tokens`) whose logits are wanted."""
+    `tokens`) whose logits are wanted.  `tokens` is a sequence of ids, or one `DeviceToken`."""
     request: Hashable
-    tokens: Sequence[int]
+    tokens: object
     want: Sequence[int] = ()
 
 
@@ -71,6 +87,19 @@ def _resolve_device(device) -> torch.device:
     dev = torch.device("cuda", int(device))
     torch.cuda.set_device(dev)
     return dev
+
+
+def fill_device_tokens(token_ids: torch.Tensor, on_device) -> None:
+    """Copies device-resident token ids into their rows of `token_ids` (device to device)."""
+    if not on_device:
+        return
+    src = on_device[0][1].tensor
+    if len(on_device) == token_ids.shape[0] and all(d.tensor is src and d.index == r for r, d in on_device) \
+            and src.shape[0] == token_ids.shape[0]:
+        token_ids.copy_(src)                              # the whole batch, in the sampler's order
+        return
+    for r, d in on_device:
+        token_ids[r:r + 1].copy_(d.tensor[d.index:d.index + 1])
 
 
 class PinnedStager:
@@ -150,6 +179,13 @@ class Engine:
         self._requests: Dict[Hashable, int] = {}
         self.steps_run = 0
         self.stager = PinnedStager(self.device)
+        # the word that a timed-out barrier wait inside a tensor-core kernel sets; its value travels to pinned
+        # memory after every step, without a synchronisation, and is looked at before the next step
+        self._kernel_status = self._kernel_status_host = None
+        if self.precision.compute == torch.bfloat16:
+            from ..csrc import gemm_fast
+            self._kernel_status = gemm_fast.status_flag(self.device)
+            self._kernel_status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.plan_builder = self._flash_plan if self.precision.compute == torch.bfloat16 else None
         from .graphs import model_is_graph_safe
         self.decode_graphs = bool(decode_graphs) and model_is_graph_safe(self.model)
@@ -171,9 +207,10 @@ class Engine:
         return request in self._requests
 
     def request_length(self, request: Hashable) -> int:
-        return int(self.cache.books.length[self._slot(request)])
+        return int(self.cache.books.length[self.slot_of(request)])
 
-    def _slot(self, request: Hashable) -> int:
+    def slot_of(self, request: Hashable) -> int:
+        """The request's slot: its row in the block tables and state arrays."""
         try:
             return self._requests[request]
         except KeyError:
@@ -185,7 +222,7 @@ class Engine:
     def _flash_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int, head_dim: int):
         from ..csrc import attention_fast, ops
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        tc = attention_fast.tc_prefill_supported(head_dim, n_heads // n_kv_heads) and ops._forced["attention"] != "flash_cp"
+        tc = attention_fast.tc_prefill_supported(head_dim, n_heads // n_kv_heads) and ops.forced("attention") != "flash_cp"
         return attention_fast.build_plan(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens, window,
                                          n_heads, n_kv_heads, sms, self.stager.upload, prefill_rows=128 if tc else 64)
 
@@ -197,16 +234,17 @@ class Engine:
         seen = set()
         take = [0] * len(books.groups)
         for e in entries:
-            slot = self._slot(e.request)
+            slot = self.slot_of(e.request)
             if e.request in seen:
                 raise EngineError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
             n = len(e.tokens)
             if n < 1:
                 raise EngineError(f"request {e.request!r} brings no tokens")
-            for tok in e.tokens:
-                if not 0 <= int(tok) < self.vocab:
-                    raise TokenOutOfRange(f"token id {tok} is outside the vocabulary of {self.vocab}")
+            if not isinstance(e.tokens, DeviceToken):       # a sampler's output is inside the vocabulary
+                for tok in e.tokens:
+                    if not 0 <= int(tok) < self.vocab:
+                        raise TokenOutOfRange(f"token id {tok} is outside the vocabulary of {self.vocab}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise EngineError(f"wanted place {w} is outside the {n} tokens of request {e.request!r}")
@@ -230,9 +268,25 @@ class Engine:
         of the entries and of their `want`, or None when nothing is wanted."""
         if not entries:
             return None
+        self._check_kernel_status()
         self.check_step(entries)
+        try:
+            return self._run_step(entries)
+        finally:
+            if self._kernel_status is not None:
+                self._kernel_status_host.copy_(self._kernel_status, non_blocking=True)
+
+    def _check_kernel_status(self) -> None:
+        if self._kernel_status_host is not None and int(self._kernel_status_host[0]) != 0:
+            torch.cuda.synchronize(self.device)
+            self._kernel_status.zero_()
+            self._kernel_status_host.zero_()
+            raise KernelTimeout("a tensor-core kernel gave up waiting on a barrier in an earlier step; "
+                                "the logits and the cache since then are invalid")
+
+    def _run_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         books = self.cache.books
-        slots = [self._slot(e.request) for e in entries]
+        slots = [self.slot_of(e.request) for e in entries]
         for s in slots:
             books.release_passed(s)
         starts = [int(books.length[s]) for s in slots]
@@ -243,10 +297,15 @@ class Engine:
         n = sum(len(e.tokens) for e in entries)
         meta = np.empty((3, n), dtype=np.int32)
         q_starts, q_lens, rows = [], [], []
+        on_device = []                                    # (row, DeviceToken): ids filled in on the device
         r = 0
         for s, st, e in zip(slots, starts, entries):
             m = len(e.tokens)
-            meta[0, r:r + m] = np.asarray(e.tokens, dtype=np.int32)
+            if isinstance(e.tokens, DeviceToken):
+                meta[0, r] = 0
+                on_device.append((r, e.tokens))
+            else:
+                meta[0, r:r + m] = np.asarray(e.tokens, dtype=np.int32)
             meta[1, r:r + m] = np.arange(st, st + m, dtype=np.int32)
             meta[2, r:r + m] = s
             rows.extend(r + int(w) for w in e.want)
@@ -259,8 +318,9 @@ class Engine:
             if g is None:
                 g = self._graphs[n] = DecodeGraph(self, n)
             self.steps_run += 1
-            return g.run(meta, slots, starts)
+            return g.run(meta, slots, starts, on_device)
         meta_dev = self.stager.upload(meta)
+        fill_device_tokens(meta_dev[0], on_device)
         ctx = StepContext(self.precision, n, meta_dev[0], meta_dev[1], meta_dev[2], slots, q_starts, q_lens,
                           starts, plan_builder=self.plan_builder)
         x = self.model.forward(ctx, self.cache.layers)

@@ -21,6 +21,11 @@ from ..csrc import ops
 from .context import StepContext
 
 
+def fill_device_tokens(token_ids, on_device):
+    from .engine import fill_device_tokens as fill
+    fill(token_ids, on_device)
+
+
 class DecodeGraph:
     def __init__(self, engine, batch: int):
         self.engine = engine
@@ -80,14 +85,16 @@ class DecodeGraph:
                            [1] * b, list(starts), plan_builder=builder)
 
     # -- capture and replay ---------------------------------------------------------------------
-    def run(self, meta: np.ndarray, slots, starts) -> torch.Tensor:
-        """meta: int32 [3, B] (token ids, positions, slots).  Returns the logits [B, vocab]."""
+    def run(self, meta: np.ndarray, slots, starts, on_device=()) -> torch.Tensor:
+        """meta: int32 [3, B] (token ids, positions, slots); `on_device`: (row, DeviceToken) pairs whose ids are
+        copied in on the device.  Returns the logits [B, vocab]."""
         eng = self.engine
         ctx = self._context(slots, starts)
         self._cursor = 3 * self.batch
         if self.graph is None:
             self._immediate = True
             self.meta.copy_(eng.stager.upload(meta))
+            fill_device_tokens(self.meta[0], on_device)
             # an eager pass first: loads libraries, sets kernel attributes, builds the plans (whose
             # uploads must not be captured); it recomputes this very step, so the cache ends up the same
             x = eng.model.forward(ctx, eng.cache.layers)
@@ -111,6 +118,7 @@ class DecodeGraph:
             if self._cursor != 3 * self.batch + sum(n for _, n in self.layout):
                 raise RuntimeError("a decode step's attention plans do not have the captured shape")
             self.static[:host.size].copy_(eng.stager.upload(host))
+            fill_device_tokens(self.meta[0], on_device)
         self.graph.replay()
         ops.count_launches(self.kernels)
         return self.logits.clone()      # the static buffer is overwritten by the next replay

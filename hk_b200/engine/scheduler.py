@@ -24,9 +24,11 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence
 
+import torch
+
 from ..cache.pages import OutOfPages
 from ..sampling import Sampler, SamplingParams, SamplingState
-from .engine import StepEntry
+from .engine import DeviceToken, StepEntry
 
 WAITING, PREFILL, DECODE, FINISHED = "waiting", "prefill", "decode", "finished"
 
@@ -62,11 +64,19 @@ class SchedulerStats:
     preemptions: int = 0
     finished: int = 0
     d2h_bytes: int = 0
+    ahead_steps: int = 0          # decode steps launched before the previous step's tokens were read
+
+
+@dataclass
+class _SampledTokens:
+    device: object                 # int32 [n] where the sampler wrote them
+    host: object                   # the same in pinned host memory once `event` has passed
+    event: object
 
 
 class Scheduler:
     def __init__(self, engine, sampler=None, max_batch_tokens: Optional[int] = None, prefill_chunk: int = 512,
-                 eos_token_ids: Sequence[int] = ()):
+                 eos_token_ids: Sequence[int] = (), run_ahead: bool = True):
         self.engine = engine
         self.books = engine.cache.books
         self.sampler = sampler if sampler is not None else Sampler(engine.device)
@@ -77,6 +87,10 @@ class Scheduler:
         self.running: List[Request] = []
         self.finished: Dict[int, Request] = {}
         self.stats = SchedulerStats()
+        self.run_ahead = bool(run_ahead)
+        self._unread = None            # (requests, their sampled tokens) not read by the host yet
+        self._ring = [None] * 4        # pinned buffers with events for the sampled tokens on their way to the host
+        self._ring_next = 0
         self._next_id = 0
         self._admissions = 0
 
@@ -118,7 +132,7 @@ class Scheduler:
 
     # -- one scheduling step -------------------------------------------------------------------
     def has_work(self) -> bool:
-        return bool(self.queue or self.running)
+        return bool(self.queue or self.running or self._unread is not None)
 
     def _pages_for(self, n_tokens: int) -> int:
         return -(-n_tokens // self.books.page_tokens)
@@ -147,7 +161,7 @@ class Scheduler:
         budget = self.max_batch_tokens
         for r in self.running:
             if r.state == DECODE and budget > 0:
-                slot = self.engine._slot(r.id)
+                slot = self.engine.slot_of(r.id)
                 self.books.release_passed(slot)
                 take = self.books.pages_to_take(slot, 1)
                 plan.append((r, [r.pending], True, take))
@@ -164,7 +178,7 @@ class Scheduler:
             for r in prefilling:
                 toks = r.tokens()
                 n = min(len(toks) - r.fed, share, self.prefill_chunk, budget)
-                slot = self.engine._slot(r.id)
+                slot = self.engine.slot_of(r.id)
                 self.books.release_passed(slot)
                 # shorten to what the free pages hold, counting the room left in the request's last page
                 room = min(free, default=1 << 30) * self.books.page_tokens + (-int(self.books.length[slot])) % self.books.page_tokens
@@ -198,8 +212,21 @@ class Scheduler:
         self.stats.finished += 1
 
     def step(self) -> List[Request]:
-        """Admits, plans, runs one engine step, samples, advances.  Returns the requests that
-        finished in this step."""
+        """One scheduling step: admits, plans, runs one engine step and samples.  Returns the requests
+        found finished in this call.
+
+        With `run_ahead`, sampled tokens are left on the device and read one call later: when the next step
+        is again pure decoding of the same requests, it is launched first (fed from the device tensor) and
+        the host reads the earlier tokens while the GPU already works.  An end token is then seen one step
+        late; the extra token computed for that request is dropped with it."""
+        done: List[Request] = []
+        if self._unread is not None:
+            reqs, toks = self._unread
+            ahead = self._launch_ahead(reqs, toks) if self._ahead_possible(reqs) else None
+            done = self._consume(reqs, toks, fed_already=ahead is not None)
+            self._unread = ahead
+            if ahead is not None:
+                return done
         self._admit()
         while True:
             plan, short = self._plan()
@@ -211,7 +238,7 @@ class Scheduler:
             if self.running:
                 # nothing fits although requests run: free the newest and try again next step
                 self._preempt(max(self.running, key=lambda r: r.admitted_at))
-            return []
+            return done
         entries = [StepEntry(r.id, toks, [len(toks) - 1] if want else []) for r, toks, want, _ in plan]
         logits = self.engine.step(entries)
         self.stats.steps += 1
@@ -224,27 +251,86 @@ class Scheduler:
             else:
                 r.fed += len(toks)
                 self.stats.prompt_tokens += len(toks)
-        done: List[Request] = []
         if wanted:
-            tokens = self.sampler.sample(logits, [r.sampling for r in wanted]).tolist()
-            self.stats.d2h_bytes += 4 * len(tokens)
-            for r, tok in zip(wanted, tokens):
-                tok = int(tok)
-                self.sampler.accept(r.sampling, tok)
-                if tok in self.eos:
-                    self._finish(r, "stop")
-                    done.append(r)
-                    continue
-                r.output.append(tok)
-                if len(r.output) >= r.max_new_tokens:
-                    self._finish(r, "length")
-                    done.append(r)
-                elif len(r.prompt) + len(r.output) > self.engine.max_context:
-                    self._finish(r, "context")
-                    done.append(r)
-                else:
-                    r.pending = tok
-                    r.state = DECODE
+            self._unread = (wanted, self._sample(logits, wanted))
+            if not self.run_ahead:
+                reqs, toks = self._unread
+                self._unread = None
+                done += self._consume(reqs, toks, fed_already=False)
+        return done
+
+    # -- tokens that are sampled but not read yet ------------------------------------------------------
+    def _ahead_possible(self, reqs: List[Request]) -> bool:
+        """True when the next step can be launched before the unread tokens are known: nothing waits, exactly
+        the requests that just sampled keep decoding, none of them can end on a count, none needs its history
+        for penalties, and the pool has the pages."""
+        if not self.run_ahead or self.queue or len(reqs) != len(self.running):
+            return False
+        take = [0] * len(self.books.groups)
+        for r, q in zip(reqs, self.running):
+            if r is not q or r.state != DECODE or r.pending is not None or r.sampling.params.adjusts_logits:
+                return False
+            total = len(r.prompt) + len(r.output) + 1          # with the unread token
+            if len(r.output) + 2 > r.max_new_tokens or total + 1 > self.engine.max_context:
+                return False
+            slot = self.engine.slot_of(r.id)
+            self.books.release_passed(slot)
+            for gi, k in enumerate(self.books.pages_to_take(slot, 1)):
+                take[gi] += k
+        return len(reqs) <= self.max_batch_tokens and all(k <= f for k, f in zip(take, self.books.free_pages()))
+
+    def _launch_ahead(self, reqs: List[Request], toks):
+        entries = [StepEntry(r.id, DeviceToken(toks.device, i), [0]) for i, r in enumerate(reqs)]
+        logits = self.engine.step(entries)
+        self.stats.steps += 1
+        self.stats.decode_tokens += len(reqs)
+        self.stats.ahead_steps += 1
+        for r in reqs:
+            r.fed += 1
+        return reqs, self._sample(logits, reqs)
+
+    def _sample(self, logits, reqs: List[Request]) -> "_SampledTokens":
+        """Samples on the device and starts the copy to the host at once: a copy started later would queue
+        behind whatever step is launched in between."""
+        toks = self.sampler.sample(logits, [r.sampling for r in reqs])
+        if not toks.is_cuda:
+            return _SampledTokens(toks, toks, None)
+        i = self._ring_next
+        self._ring_next = (i + 1) % len(self._ring)
+        if self._ring[i] is None or self._ring[i][0].numel() < toks.numel():
+            self._ring[i] = (torch.empty(max(64, toks.numel()), dtype=toks.dtype).pin_memory(), torch.cuda.Event())
+        host, event = self._ring[i]
+        host = host[:toks.numel()]
+        host.copy_(toks, non_blocking=True)
+        event.record()
+        return _SampledTokens(toks, host, event)
+
+    def _consume(self, reqs: List[Request], toks, fed_already: bool) -> List[Request]:
+        """Reads sampled tokens from the device and advances their requests."""
+        done: List[Request] = []
+        if toks.event is not None:
+            toks.event.synchronize()
+        tokens = toks.host.tolist()
+        self.stats.d2h_bytes += 4 * len(tokens)
+        for r, tok in zip(reqs, tokens):
+            if r.state == FINISHED:                 # ended (an end token, a cancel) while this token was in flight
+                continue
+            tok = int(tok)
+            self.sampler.accept(r.sampling, tok)
+            if tok in self.eos:
+                self._finish(r, "stop")
+                done.append(r)
+                continue
+            r.output.append(tok)
+            if len(r.output) >= r.max_new_tokens:
+                self._finish(r, "length")
+                done.append(r)
+            elif len(r.prompt) + len(r.output) > self.engine.max_context:
+                self._finish(r, "context")
+                done.append(r)
+            else:
+                r.pending = None if fed_already else tok
+                r.state = DECODE
         return done
 
     def run(self) -> Dict[int, Request]:

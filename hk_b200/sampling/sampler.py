@@ -84,7 +84,8 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, states: Sequence[SamplingState]) -> torch.Tensor:
         """logits: float32 [rows, vocab] on the device (modified in place by penalties).
-        Returns int32 [rows] on the device; the caller records the tokens with `accept`."""
+        Returns int32 [rows] on the device and advances each state's draw counter; the caller records
+        the tokens with `accept` once it has read them."""
         rows = logits.shape[0]
         if rows != len(states):
             raise ValueError("one sampling state per row of logits")
@@ -93,6 +94,8 @@ class Sampler:
             self._adjust(logits, states)
         if all(s.params.greedy for s in states):
             ops.argmax(logits, out)
+            for s in states:
+                s.drawn += 1
             return out
         f = np.empty((3, rows), dtype=np.float32)
         k = np.empty(rows, dtype=np.int32)
@@ -106,6 +109,8 @@ class Sampler:
         kd = torch.from_numpy(k).to(self.device)
         scd = torch.from_numpy(sc).to(self.device)
         ops.sample(logits, fd[0], kd, fd[1], fd[2], scd[0], scd[1], out)
+        for s in states:
+            s.drawn += 1          # the draw is made: the next one uses the next counter, whether or not this token has been read
         return out
 
     def _adjust(self, logits: torch.Tensor, states: Sequence[SamplingState]) -> None:
@@ -139,5 +144,5 @@ class Sampler:
 
     @staticmethod
     def accept(state: SamplingState, token: int) -> None:
+        """Records a drawn token once the host has read it (the history feeds the penalties)."""
         state.history.append(int(token))
-        state.drawn += 1

@@ -62,6 +62,27 @@ def test_bfloat16_greedy_generation_agrees_where_the_margin_is_clear(tmp_path):
             ids.append(tok)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_ahead_decoding_gives_the_same_tokens(tmp_path, dtype):
+    """Decode steps launched before the earlier tokens are read (ids handed over on the device) against
+    the step-by-step order: greedy and seeded sampling, an end token in the middle, a tight pool."""
+    import hk_b200
+    from hk_b200.api import GenerationStats, generate_with_engine
+    d = helpers.make_model_dir(tmp_path, "A", torch.float32 if dtype == "float32" else torch.bfloat16)
+    prompts = helpers.prompts_for("A", np.random.default_rng(8), [3, 21, 40, 9])
+    eng = hk_b200.Engine(d, dtype=dtype, max_tokens=384, max_requests=4, max_context=96)
+    for kw in (dict(temperature=0), dict(temperature=0.9, top_k=20, top_p=0.9, seed=11)):
+        base = generate_with_engine(eng, prompts, 40, run_ahead=False, eos_token_ids=(), **kw)
+        st = GenerationStats()
+        assert generate_with_engine(eng, prompts, 40, run_ahead=True, eos_token_ids=(), stats=st, **kw) == base
+        assert st.decode_steps >= 39
+        # an end token taken from the middle of one request's output: that request stops there, the others go on
+        eos = base[1][17]
+        cut = [o[:o.index(eos)] if eos in o else o for o in base]
+        assert generate_with_engine(eng, prompts, 40, run_ahead=True, eos_token_ids=(eos,), **kw) == cut
+    assert eng.free_pages() == [eng.cache.books.groups[0].pool.num_pages] * len(eng.cache.books.groups)
+
+
 def test_native_engine_forward_and_rewind(model_b):
     import hk_b200
     d, cfg, w = model_b
@@ -128,6 +149,27 @@ def test_step_errors_leave_the_engine_usable(model_b):
     got = eng.step([StepEntry("a", ids[:3], [2])])[0].double().cpu().numpy()
     ref = P.forward(cfg, w, ids + ids[:3])[-1]
     assert np.abs(got - ref).max() < 2e-5 * np.abs(ref).max()
+
+
+def test_a_recorded_kernel_timeout_is_raised_at_the_next_step_and_cleared(tmp_path):
+    """The status word that a timed-out barrier wait would set is written from the host here (no kernel is
+    made to wait): the engine raises at the step after the one that carried it, then works again."""
+    from hk_b200.csrc import gemm_fast
+    from hk_b200.engine import Engine, KernelTimeout, StepEntry
+    d = helpers.make_model_dir(tmp_path, "A", torch.bfloat16)
+    eng = Engine(d, dtype="bfloat16", max_tokens=128)
+    eng.open_request("a")
+    first = eng.step([StepEntry("a", [1, 2, 3], [2])]).clone()
+    gemm_fast.status_flag(eng.device).fill_(1)
+    eng.step([StepEntry("a", [4], [0])])
+    torch.cuda.synchronize()
+    with pytest.raises(KernelTimeout):
+        eng.step([StepEntry("a", [5], [0])])
+    assert eng.request_length("a") == 4              # the refused step changed nothing
+    eng.close_request("a")
+    eng.open_request("a")
+    assert torch.equal(eng.step([StepEntry("a", [1, 2, 3], [2])]), first)
+    gemm_fast.check_status(eng.device)
 
 
 # ---- the sampler -------------------------------------------------------------------------------

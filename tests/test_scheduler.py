@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from hk_b200.cache import CacheBooks
+from hk_b200.engine import DeviceToken
 from hk_b200.engine.scheduler import RequestRefused, Scheduler
 from hk_b200.sampling import GREEDY, SamplingParams
 
@@ -33,7 +34,7 @@ class FakeEngine:
         self.cache.books.close(self.slots.pop(rid))
         del self.fed[rid]
 
-    def _slot(self, rid):
+    def slot_of(self, rid):
         return self.slots[rid]
 
     def step(self, entries):
@@ -41,7 +42,8 @@ class FakeEngine:
         rows = []
         for e in entries:
             self.cache.books.extend(self.slots[e.request], len(e.tokens))
-            for i, t in enumerate(e.tokens):
+            toks = [int(e.tokens.tensor[e.tokens.index])] if isinstance(e.tokens, DeviceToken) else e.tokens
+            for i, t in enumerate(toks):
                 self.fed[e.request].append(int(t))
                 if i in e.want:
                     row = torch.zeros(VOCAB)
@@ -71,9 +73,9 @@ def expected(prompt, n):
     return out
 
 
-def make(prefill_chunk=8, **kw):
+def make(prefill_chunk=8, run_ahead=True, **kw):
     eng = FakeEngine(**kw)
-    return eng, Scheduler(eng, sampler=CpuSampler(), prefill_chunk=prefill_chunk)
+    return eng, Scheduler(eng, sampler=CpuSampler(), prefill_chunk=prefill_chunk, run_ahead=run_ahead)
 
 
 def test_decodes_first_then_prompt_portions_within_the_budget():
@@ -179,6 +181,64 @@ def test_many_requests_over_few_slots_all_finish_in_order_of_arrival():
         assert done[rid].output == expected(p, 3 + i % 4)
     assert max(len(st) for st in eng.log) <= 3
     assert eng.cache.books.free_pages() == [12]
+
+
+def test_run_ahead_launches_the_next_decode_before_reading_and_drops_the_token_after_an_end():
+    eng, s = make(num_pages=32, max_context=64)
+    p = [3, 1, 4]
+    want = expected(p, 12)
+    s.eos = {want[6]}
+    a = s.submit(p, 12, GREEDY)
+    done = s.run()
+    assert done[a].finish_reason == "stop" and done[a].output == want[:6]
+    # the end token (the 7th) is read one step late: one more decode step ran with it and its result is dropped
+    decodes = [st for st in eng.log if st == [(a, 1, [0])]]
+    assert len(decodes) == 7
+    assert eng.cache.books.free_pages() == [32] and not eng.slots and not s.has_work()
+    # without run-ahead: same output, one step fewer
+    eng2, s2 = make(num_pages=32, max_context=64, run_ahead=False)
+    s2.eos = {want[6]}
+    a2 = s2.submit(p, 12, GREEDY)
+    assert s2.run()[a2].output == want[:6]
+    assert len([st for st in eng2.log if st == [(a2, 1, [0])]]) == 6
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_run_ahead_changes_no_output_under_random_arrivals_tight_pages_and_limits(seed):
+    import random
+    outs = []
+    for ahead in (False, True):
+        rnd = random.Random(seed)
+        eng, s = make(num_pages=10, page_tokens=4, max_requests=3, max_context=24, max_batch_tokens=12, run_ahead=ahead,
+                      windows=(None, 6) if seed % 2 else (None,))
+        s.eos = {7, 23}
+        ids, prompts = [], {}
+        for step in range(200):
+            if rnd.random() < 0.25 and len(ids) < 14:
+                pr = [rnd.randrange(VOCAB) for _ in range(rnd.randint(1, 14))]
+                rid = s.submit(pr, rnd.randint(1, 12), GREEDY)
+                ids.append(rid)
+                prompts[rid] = pr
+            if rnd.random() < 0.03 and ids:
+                s.cancel(rnd.choice(ids))
+            s.step()
+            eng.cache.books.audit()
+        done = s.run()
+        assert (s.stats.ahead_steps > 0) == ahead
+        assert not eng.slots and all(f == 10 for f in eng.cache.books.free_pages())
+        outs.append({rid: (done[rid].output, done[rid].finish_reason) for rid in ids})
+        for rid in ids:
+            out, why = outs[-1][rid]
+            if why != "cancelled":
+                full = expected(prompts[rid], len(out) + 1)
+                assert out == full[:len(out)]
+                if why == "stop":
+                    assert full[len(out)] in s.eos
+    # cancellations land at different moments of a request's life in the two modes; everything else is equal
+    for rid, (out, why) in outs[0].items():
+        out2, why2 = outs[1][rid]
+        if "cancelled" not in (why, why2):
+            assert (out, why) == (out2, why2)
 
 
 def test_sampling_params_defaults_are_the_references():
