@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
     "gemm_smallm": "gemm_smallm.cu",
+    "gemm_stream": "gemm_stream.cu",
     "attention_flash": "attention_flash.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
 }

@@ -92,6 +92,71 @@ def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
     return bn, splits
 
 
+STREAM_M = 32         # the most rows the persistent streaming kernel takes
+STREAM_M_AUTO = 8     # up to here it is chosen
+STREAM_MIN_WEIGHTS = 40 << 20    # ... for weights of at least this many elements (see `stream_row_warps`)
+_stream_rw = 0        # tests and tuning runs may pin the consumer warps across a tile's rows (8, 4, 2, 1)
+_stream_ctas = 0      # tests may run fewer CTAs than SMs to move the places where CTAs hand a tile over
+_stream_scratch = {}
+
+
+STREAM_MAX_N = 1 << 20
+
+
+def _stream_buffers(device: torch.device, lib):
+    """Workspace for partial tiles and the per-tile arrival counters of the streaming kernel, sized once for
+    the largest call it takes and never replaced (captured graphs keep their addresses).  One pair per device:
+    the engine launches on one stream, and launches that do not overlap may share them."""
+    key = device.index or 0
+    if key not in _stream_scratch:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        lib.hk_gemm_stream_workspace.restype = ctypes.c_longlong
+        ws = torch.empty(int(lib.hk_gemm_stream_workspace(STREAM_M, 8)), dtype=torch.float32, device=device)
+        ct = torch.zeros(STREAM_MAX_N // 16 + 2, dtype=torch.int32, device=device)
+        _stream_scratch[key] = (ws, ct)
+    return _stream_scratch[key]
+
+
+def stream_row_warps(N: int, sms: int) -> int:
+    """Consumer warps across a tile's rows (tile = 16 rows each): the widest tile that still gives every CTA a
+    whole tile of its own, so that only the left-over tiles are shared between CTAs."""
+    if _stream_rw:
+        return _stream_rw
+    for rw in (4, 2):
+        if -(-N // (16 * rw)) >= sms:
+            return rw
+    return 1
+
+
+def stream_wanted(M: int, N: int, K: int) -> bool:
+    """The streaming kernel pays about two microseconds to fill its ring and to hand shared tiles over; measured
+    on the 8B model's decode products it wins from about 80 MB of weights up (gate/up, down, output head) and
+    loses to the small-M kernel below (q/k/v, o)."""
+    return M <= STREAM_M_AUTO and N * K >= STREAM_MIN_WEIGHTS and K % 64 == 0
+
+
+def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
+    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up over the paired layout."""
+    from . import ops
+    M, K = a.shape
+    N = w.shape[0]
+    if M > STREAM_M or N > STREAM_MAX_N:
+        return False
+    lib = build.load("gemm_stream")
+    scratch = _stream_buffers(a.device, lib)
+    if scratch is None:
+        return False
+    ws, ct = scratch
+    code = lib.hk_gemm_stream(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(ldo), epilogue,
+                              stream_row_warps(N, _sms(a.device)),
+                              _ptr(ws), _ptr(ct), _ptr(status_flag(a.device)), _stream_ctas, _stream())
+    if code == _UNSUPPORTED:
+        return False
+    ops._check(code, "gemm (streaming)")
+    return True
+
+
 def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     """out (fp32) = a w^T (+ out).  Returns False when no tensor-core kernel takes the shape."""
     from . import ops
@@ -99,6 +164,11 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     N = w.shape[0]
     if not _aligned(a, w):
         return False
+    if choice == "stream" or (choice is None and stream_wanted(M, N, K)):
+        if run_stream(a, w, out, 1 if accumulate else 0, N):
+            return True
+        if choice == "stream":
+            return False
     if choice == "smallm" or (choice is None and M <= SMALL_M_AUTO):
         if M > SMALL_M:
             return False
@@ -121,14 +191,22 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     return True
 
 
-def run_swiglu(a, w_paired, out) -> bool:
+def run_swiglu(a, w_paired, out, choice: Optional[str] = None) -> bool:
     """out (bf16 [M, F]) = silu(gate) * up of a w^T, for a weight laid out [128 gate | 128 up] per
-    256 rows (see `pair_gate_up`).  tcgen05 kernel only; False when it refuses."""
+    256 rows (see `pair_gate_up`), in the epilogue of the streaming kernel (few rows) or of the tcgen05
+    kernel; False when they refuse."""
     from . import ops
     M, K = a.shape
     N = w_paired.shape[0]
     if not _aligned(a, w_paired) or N % 256 or out.shape[1] % 8:
         return False
+    if choice == "stream" or (choice is None and stream_wanted(M, N, K)):
+        if run_stream(a, w_paired, out, 2, out.shape[1]):
+            return True
+        if choice == "stream":
+            return False
+    if choice is None and M <= SMALL_M_AUTO:
+        return False             # few rows, small weights: the small-M product and the swiglu kernel
     lib = build.load("gemm_tc")
     _, splits = tc_config(M, N, K, _sms(a.device), bn=256)
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else None

@@ -88,7 +88,7 @@ def forced(kind: str) -> Optional[str]:
 
 @contextlib.contextmanager
 def force(gemm: Optional[str] = None, attention: Optional[str] = None):
-    """Pins the kernel family inside the block: gemm in {'generic','tc','smallm'},
+    """Pins the kernel family inside the block: gemm in {'generic','tc','smallm','stream'},
     attention in {'generic','flash','flash_cp'} ('flash_cp': the flash kernels without the TMA-fed decode
     variant).  A pinned kernel that refuses the shape raises."""
     old = dict(_forced)
@@ -159,11 +159,6 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), _stream()), "swiglu")
 
 
-def gemm_fast_small_m() -> int:
-    from . import gemm_fast
-    return gemm_fast.SMALL_M_AUTO
-
-
 def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, block: int) -> None:
     """out[M, F] = silu(gate) * up of a @ w_paired^T, w_paired [2F, K] laid out [block gates | block ups |
     ...] (block = 0: [F gates | F ups]).  Fused into the tensor-core product's epilogue when that takes the
@@ -174,9 +169,9 @@ def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, bloc
     M, F = out.shape
     if a.shape[0] != M or w_paired.shape != (2 * F, a.shape[1]):
         raise KernelError("gemm_swiglu: shapes do not fit")
-    if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc") and (M > gemm_fast_small_m() or _forced["gemm"] == "tc"):
+    if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc", "stream"):
         from . import gemm_fast
-        if block == gemm_fast.PAIR and gemm_fast.run_swiglu(a, w_paired, out):
+        if block == gemm_fast.PAIR and gemm_fast.run_swiglu(a, w_paired, out, _forced["gemm"]):
             return
     gu = torch.empty((M, 2 * F), dtype=torch.float32, device=a.device)
     gemm(a, w_paired, gu)

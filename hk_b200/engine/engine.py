@@ -160,7 +160,7 @@ class Engine:
         from ..csrc import build as _build
         needed = ["elementwise", "gemm_generic", "attention_generic"]
         if self.precision.compute == torch.bfloat16:
-            needed += ["gemm_smallm", "gemm_tc", "attention_flash", "attention_prefill_tc"]
+            needed += ["gemm_smallm", "gemm_stream", "gemm_tc", "attention_flash", "attention_prefill_tc"]
         _build.build_many(needed)
         self.model = build_model(config, self.max_context)
         specs = self.model.param_specs()

@@ -1,13 +1,15 @@
 """Single-kernel cases with device timing: `python -m hk_b200.profiling <case> [sizes]`.
 
 Each case sets up one hot kernel of the engine at a serving size, runs it a few times, times it
-with CUDA events (L2 flushed between runs by writing a buffer larger than L2) and prints the
+with CUDA events (L2 flushed between runs by reading a buffer larger than L2) and prints the
 achieved GB/s or TFLOP/s.  The same command under `ncu -k regex:<kernel>` gives the hardware
 counters for that kernel.  (The reference has per-kernel event timing of the same kind behind
 HK_CUDA_EVENTS: src/cuda.zig:1212-1263.)
 
-Cases: gemm_tc (tcgen05 product, --swiglu / --add), gemm_smallm (decode product), attn_decode
-(paged decode attention), attn_prefill (paged causal attention of one prompt).
+Cases: gemm_tc (tcgen05 product, --swiglu / --add), gemm_smallm and gemm_stream (decode products), attn_decode
+(paged decode attention), attn_prefill (paged causal attention of one prompt), decode (whole decode steps
+of a shallow random model with the 8B layer sizes, launched one kernel after the other without a graph: the
+launch list of a profiler then shows every kernel of a step with its time).
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ import torch
 def _time(fn, reps: int, flush: torch.Tensor):
     times = []
     for i in range(reps + 2):
-        flush.zero_()
+        flush.max()           # reading a buffer larger than L2 leaves it full of clean lines that are not the case's
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -41,9 +43,38 @@ def _paged(batch, ctx, G, hd, pt, dev):
     return k, v, perm.contiguous()
 
 
+def _decode_steps(a, dev) -> int:
+    from .config import config_from_dict
+    from .engine import Engine, StepEntry
+    cfg = config_from_dict(dict(architectures=["Qwen3ForCausalLM"], hidden_size=a.hidden, num_hidden_layers=a.layers,
+                                intermediate_size=a.intermediate, num_attention_heads=a.heads, num_key_value_heads=a.kv_heads,
+                                head_dim=a.head_dim, vocab_size=a.vocab, rope_theta=1e6, rms_norm_eps=1e-6,
+                                tie_word_embeddings=False, max_position_embeddings=8192, initializer_range=0.02))
+    per = -(-(a.ctx + 64) // 64) * 64
+    eng = Engine(config=cfg, random_seed=2, dtype="bfloat16", max_tokens=a.batch * per, page_tokens=a.page_tokens,
+                 max_requests=a.batch, max_context=8192, max_batch_tokens=8192, decode_graphs=False)
+    rng = np.random.default_rng(0)
+    ids = list(range(a.batch))
+    for r in ids:
+        eng.open_request(r)
+    group = max(1, 8192 // a.ctx)
+    for i in range(0, a.batch, group):
+        eng.step([StepEntry(r, rng.integers(0, a.vocab, a.ctx).tolist(), []) for r in ids[i:i + group]])
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for s in range(a.reps):
+        if s == a.reps - 1:
+            t0.record()
+        eng.step([StepEntry(r, [int(rng.integers(0, a.vocab))], [0]) for r in ids])
+    t1.record()
+    torch.cuda.synchronize()
+    print(f"decode layers={a.layers} batch={a.batch} ctx={a.ctx}: last step {t0.elapsed_time(t1) * 1e3:.0f} us (no graph)")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="hk_b200.profiling")
-    ap.add_argument("case", choices=["gemm_tc", "gemm_smallm", "attn_decode", "attn_prefill"])
+    ap.add_argument("case", choices=["gemm_tc", "gemm_smallm", "gemm_stream", "attn_decode", "attn_prefill", "decode"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -56,18 +87,29 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=2, help="decode: layers of the model")
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--intermediate", type=int, default=12288)
+    ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--cluster", type=int, default=0, help="gemm_smallm: pin the CTAs per cluster that split K (1, 2 or 4)")
     ap.add_argument("--mma", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
+    ap.add_argument("--row-warps", type=int, default=0, help="gemm_stream: consumer warps across a tile's rows (8, 4, 2 or 1)")
+    ap.add_argument("--ctas", type=int, default=0, help="gemm_stream: run this many CTAs instead of one per SM")
     ap.add_argument("--row-tiles", type=int, default=0, help="gemm_smallm: pin the row tiles of 16 per CTA (1, 2 or 4)")
     a = ap.parse_args(argv)
     from .csrc import attention_fast, gemm_fast, ops
     gemm_fast._rt_override = a.row_tiles
     gemm_fast._cs_override = a.cluster
+    gemm_fast._stream_ctas = a.ctas
+    if a.row_warps:
+        gemm_fast._stream_rw = a.row_warps
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than the 126 MB L2
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)      # larger than the 126 MB L2
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    if a.case in ("gemm_tc", "gemm_smallm"):
+    if a.case == "decode":
+        return _decode_steps(a, dev)
+    if a.case in ("gemm_tc", "gemm_smallm", "gemm_stream"):
         x = (torch.randn(a.m, a.k, device=dev) / 8).to(torch.bfloat16)
         w = (torch.randn(a.n, a.k, device=dev) / 8).to(torch.bfloat16)
         if a.swiglu:
@@ -76,7 +118,7 @@ def main(argv=None) -> int:
         else:
             out = torch.zeros(a.m, a.n, dtype=torch.float32, device=dev)
             fn = lambda: ops.gemm(x, w, out, accumulate=a.add)
-        with ops.force(gemm="tc" if a.case == "gemm_tc" else "smallm"):
+        with ops.force(gemm={"gemm_tc": "tc", "gemm_smallm": "smallm", "gemm_stream": "stream"}[a.case]):
             us = _time(fn, a.reps, flush)
         flops = 2.0 * a.m * a.n * a.k
         nbytes = 2.0 * (a.n * a.k + a.m * a.k) + out.numel() * out.element_size()

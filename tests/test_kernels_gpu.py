@@ -325,11 +325,73 @@ def test_gemm_small_m_cluster_split_k(cs, m, n, k):
         gemm_fast._cs_override = 0
 
 
+@pytest.mark.parametrize("rw", [8, 4, 2, 1])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(16, 64), (300, 192), (1000, 4096), (4096, 12288), (6144, 512), (40, 64), (18992, 128), (2400, 320)])
+def test_gemm_stream(rw, m, n, k):
+    # the persistent streaming kernel: tiles of 128, 64, 32 or 16 weight rows; ragged N and K; CTAs that share tiles
+    from hk_b200.csrc import gemm_fast
+    if rw == 1 and m > 16:
+        pytest.skip("no such variant")
+    gemm_fast._stream_rw = rw
+    try:
+        gemm_case("stream", m, n, k, False)
+        gemm_case("stream", m, n, k, True, seed=1)
+    finally:
+        gemm_fast._stream_rw = 0
+
+
+@pytest.mark.parametrize("ctas", [1, 3, 7, 50, 148])
+@pytest.mark.parametrize("m,n,k", [(8, 1000, 4096), (5, 200, 1088), (16, 4096, 640), (3, 9536, 256)])
+def test_gemm_stream_hand_over_between_ctas_is_exact_and_repeatable(ctas, m, n, k):
+    # fewer CTAs move the places where one CTA's share of a tile ends and the next one's begins; the partial sums
+    # are added in K order whoever arrives last, so two runs agree to the bit, and the counters are left at zero
+    from hk_b200.csrc import gemm_fast
+    gemm_fast._stream_ctas = ctas
+    try:
+        gemm_case("stream", m, n, k, False)
+        gemm_case("stream", m, n, k, True, seed=3)
+        g = torch.Generator().manual_seed(11)
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+        w = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+        outs = [torch.empty(m, n, device=DEV) for _ in range(3)]
+        with ops().force(gemm="stream"):
+            for o in outs:
+                ops().gemm(a, w, o)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        assert int(gemm_fast._stream_scratch[0][1].abs().sum()) == 0
+    finally:
+        gemm_fast._stream_ctas = 0
+    gemm_fast.check_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("rw", [8, 4, 2, 1])
+@pytest.mark.parametrize("m,f,k", [(1, 128, 64), (8, 384, 192), (7, 1536, 4096), (20, 256, 1024), (32, 12288, 256)])
+def test_gemm_stream_swiglu_epilogue(rw, m, f, k):
+    from hk_b200.csrc import gemm_fast
+    if rw == 1 and m > 16:
+        pytest.skip("no such variant")
+    g = torch.Generator().manual_seed(m + f + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    up = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    out = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
+    gemm_fast._stream_rw = rw
+    try:
+        with ops().force(gemm="stream"):
+            ops().gemm_swiglu(a.to(DEV), gemm_fast.pair_gate_up(gate, up).to(DEV), out, gemm_fast.PAIR)
+    finally:
+        gemm_fast._stream_rw = 0
+    gemm_fast.check_status(torch.device(DEV))
+    want = ref_ops.swiglu(torch.cat([ref_ops.gemm(a, gate), ref_ops.gemm(a, up)], dim=1))
+    close(out, want, torch.bfloat16, atol=2e-3)
+
+
 def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
     a = torch.randn(4, 70).to(torch.bfloat16).to(DEV)      # K % 8 != 0
     w = torch.randn(9, 70).to(torch.bfloat16).to(DEV)
     out = torch.empty(4, 9, device=DEV)
-    for kernel in ("tc", "smallm"):
+    for kernel in ("tc", "smallm", "stream"):
         with pytest.raises(ops().KernelError):
             with ops().force(gemm=kernel):
                 ops().gemm(a, w, out)
@@ -339,6 +401,10 @@ def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
         with ops().force(gemm="smallm"):
             ops().gemm(torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV),
                        torch.zeros(65, 8, device=DEV))
+    with pytest.raises(ops().KernelError):
+        with ops().force(gemm="stream"):
+            ops().gemm(torch.zeros(33, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV),
+                       torch.zeros(33, 8, device=DEV))
 
 
 @pytest.mark.parametrize("m,f,k", [(128, 128, 64), (300, 384, 200), (2048, 1536, 512), (7, 256, 128), (64, 128, 64), (65, 128, 64),
