@@ -32,7 +32,7 @@ SHAPE = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_la
              rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=8192, initializer_range=0.02)
 CONTEXT = 8192
 PROMPT = 2048
-PAGE = 16
+PAGE = 64
 SEED = 2
 
 
