@@ -310,3 +310,208 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
         assert np.abs(cut[k] - want[k]).max() <= tol_max * scale
     # the state slot was cleared when the requests were opened again: the second run equals the first
     assert eng.free_pages() == [eng.cache.num_pages]
+
+
+# ---------------------------------------------------------------------------------------------
+# A second toy architecture defined here: a feed-forward with routing (each token goes to two of
+# four experts, router logits and weights in 32-bit) and a position encoding of its own (angles
+# that grow with the logarithm of the position, on part of the head).  Nothing in the package
+# knows about either; they are registered as parts and built through the architecture registry.
+
+@dataclass
+class RoutedConfig:
+    architecture: str = "ToyRoutedForCausalLM"
+    hidden_size: int = 40
+    vocab_size: int = 61
+    experts: int = 4
+    expert_width: int = 24
+    initializer_range: float = 0.2
+    max_position_embeddings: int = 96
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: v for k, v in raw.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return dict(architectures=[self.architecture], hidden_size=self.hidden_size, vocab_size=self.vocab_size,
+                    experts=self.experts, expert_width=self.expert_width, initializer_range=self.initializer_range)
+
+
+def log_angles(max_positions, rotary_dim):
+    """angle[p, i] = log(1 + p) * (i + 1), in float64."""
+    p = np.arange(max_positions, dtype=np.float64)[:, None]
+    return np.log1p(p) * (np.arange(rotary_dim // 2, dtype=np.float64)[None, :] + 1.0)
+
+
+def build_routed(cfg, max_positions):
+    from hk_b200.csrc import ops
+    from hk_b200.models import LayerCall, ModelSpec
+    from hk_b200.parts import (GQAAttention, MATRIX, VECTOR, OutputHead, ParamSpec, Part, PreNormBlock, RMSNorm,
+                               SwiGLUFeedForward, TokenEmbedding, register_part)
+
+    class LogPosition(Part):
+        """A position encoding with the rotary interface (tables of cos and sin by position) and other angles."""
+        graph_safe = True
+
+        def __init__(self, rotary_dim, max_positions):
+            self.rotary_dim, self.max_positions, self.cos, self.sin = rotary_dim, max_positions, None, None
+
+        def own_bind(self, tensors, precision):
+            a = torch.from_numpy(log_angles(self.max_positions, self.rotary_dim))
+            self.cos = torch.cos(a).float().contiguous().to(precision.device)
+            self.sin = torch.sin(a).float().contiguous().to(precision.device)
+
+        def tables(self):
+            return self.cos, self.sin, self.rotary_dim
+
+    class TopTwoRoutedFeedForward(Part):
+        """residual += sum over the token's two best experts e of p_e * down_e(silu(gate_e xb) * up_e xb), where
+        p = softmax of the two router logits; router logits in 32-bit from a 32-bit router matrix."""
+        graph_safe = False          # the rows of each expert are found on the host
+
+        def __init__(self, d, experts, width, prefix):
+            self.d, self.E, self.prefix = d, experts, prefix
+            self.router = None
+            self.expert = [SwiGLUFeedForward(d, width, f"{prefix}expert{e}.") for e in range(experts)]
+
+        def children(self):
+            return self.expert
+
+        def own_param_specs(self):
+            return {self.prefix + "router": ParamSpec((self.E, self.d), VECTOR)}      # kept in float32
+
+        def own_bind(self, tensors, precision):
+            self.router = tensors[self.prefix + "router"]
+
+        def forward(self, xb, residual, ctx):
+            n = xb.shape[0]
+            logits = torch.empty((n, self.E), dtype=torch.float32, device=xb.device)
+            ops.gemm(xb.float().contiguous(), self.router, logits)                     # 32-bit product
+            top = torch.topk(logits, 2, dim=1)
+            p = torch.softmax(top.values, dim=1)
+            for e in range(self.E):
+                for k in range(2):
+                    rows = torch.nonzero(top.indices[:, k] == e).flatten()
+                    if rows.numel() == 0:
+                        continue
+                    part = torch.zeros((rows.numel(), self.d), dtype=torch.float32, device=xb.device)
+                    self.expert[e].forward(xb[rows].contiguous(), part, ctx)
+                    residual[rows] += part * p[rows, k:k + 1]
+
+    register_part("position", "toy_log", LogPosition)
+    register_part("feed_forward", "toy_top2", TopTwoRoutedFeedForward)
+    d = cfg.hidden_size
+    pos = LogPosition(8, max_positions)          # rotates 8 of the 16 dims of a head
+    blocks = [
+        PreNormBlock(RMSNorm(d, 1e-6, "l0.n1"), GQAAttention(d, 4, 2, 16, "l0.attn.", qk_norm_eps=1e-6, position=pos),
+                     RMSNorm(d, 1e-6, "l0.n2"), TopTwoRoutedFeedForward(d, cfg.experts, cfg.expert_width, "l0.moe.")),
+        PreNormBlock(RMSNorm(d, 1e-6, "l1.n1"), GQAAttention(d, 4, 2, 16, "l1.attn.", position=pos),
+                     RMSNorm(d, 1e-6, "l1.n2"), SwiGLUFeedForward(d, 56, "l1.mlp.")),
+    ]
+    return ModelSpec(cfg, TokenEmbedding(cfg.vocab_size, d, "emb"), blocks,
+                     OutputHead(d, cfg.vocab_size, RMSNorm(d, 1e-6, "norm"), "head"), [LayerCall(0), LayerCall(1)])
+
+
+def routed_plain(cfg, w, ids):
+    """The routed toy model on whole sequences in float64; also returns the smallest gap between a token's
+    second and third router logit (a test is only meaningful where the routing is not a coin toss)."""
+    T = len(ids)
+    ang = log_angles(cfg.max_position_embeddings, 8)[:T]
+    cos, sin = np.cos(ang), np.sin(ang)
+
+    def rotate(x, heads):                                    # rotate-half on the first 8 dims of each head
+        x = x.reshape(T, heads, 16).copy()
+        a, b = x[:, :, :4].copy(), x[:, :, 4:8].copy()
+        x[:, :, :4] = a * cos[:, None, :] - b * sin[:, None, :]
+        x[:, :, 4:8] = a * sin[:, None, :] + b * cos[:, None, :]
+        return x.reshape(T, heads * 16)
+
+    def swiglu_ffn(xb, p):
+        return P.linear(P.swiglu(P.linear(xb, w[p + "gate_proj.weight"]), P.linear(xb, w[p + "up_proj.weight"])), w[p + "down_proj.weight"])
+
+    x = w["emb"][ids]
+    gap = np.inf
+    for l in (0, 1):
+        p = f"l{l}.attn."
+        xb = P.rms_norm(x, w[f"l{l}.n1"], 1e-6)
+        q, k, v = (P.linear(xb, w[p + n + "_proj.weight"]) for n in "qkv")
+        if l == 0:
+            q = P.head_norm(q, w[p + "q_norm.weight"], 16, 1e-6)
+            k = P.head_norm(k, w[p + "k_norm.weight"], 16, 1e-6)
+        x = x + P.linear(P.causal_gqa_attention(rotate(q, 4), rotate(k, 2), v, 4, 2, 16), w[p + "o_proj.weight"])
+        xb = P.rms_norm(x, w[f"l{l}.n2"], 1e-6)
+        if l == 1:
+            x = x + swiglu_ffn(xb, "l1.mlp.")
+            continue
+        logits = xb @ w["l0.moe.router"].T
+        order = np.argsort(-logits, axis=1)
+        srt = np.take_along_axis(logits, order, axis=1)
+        gap = min(gap, float((srt[:, 1] - srt[:, 2]).min()))
+        add = np.zeros_like(x)
+        for t in range(T):
+            e0, e1 = order[t, 0], order[t, 1]
+            z = np.exp(srt[t, :2] - srt[t, 0])
+            z /= z.sum()
+            for e, pe in ((e0, z[0]), (e1, z[1])):
+                add[t] += pe * swiglu_ffn(xb[t:t + 1], f"l0.moe.expert{e}.")[0]
+        x = x + add
+    return P.linear(P.rms_norm(x, w["norm"], 1e-6), w["head"]), gap
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_toy_routed_feed_forward_and_another_position_encoding(dtype):
+    from hk_b200.config import register_architecture
+    from hk_b200.engine import Engine, StepEntry
+    from hk_b200.parts import part_class
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, build_routed)
+    cfg = RoutedConfig()
+    eng = Engine(config=cfg, random_seed=5, dtype=dtype, max_tokens=192, page_tokens=8, max_requests=2, max_context=96)
+    assert part_class("feed_forward", "toy_top2").__name__ == "TopTwoRoutedFeedForward"
+    assert not eng.decode_graphs                 # the routed part is not graph-safe: this model is stepped eagerly
+    # the weights the engine computes with, by the names the parts declared
+    blk0, blk1 = eng.model.layers
+    w = {"emb": eng.model.embedding.table, "head": eng.model.head.weight, "norm": eng.model.head.norm.weight,
+         "l0.moe.router": blk0.feed_forward.router}
+    for l, blk in ((0, blk0), (1, blk1)):
+        a = blk.mixer
+        w[f"l{l}.n1"], w[f"l{l}.n2"] = blk.mixer_norm.weight, blk.ffn_norm.weight
+        w[f"l{l}.attn.q_proj.weight"], w[f"l{l}.attn.k_proj.weight"], w[f"l{l}.attn.v_proj.weight"] = \
+            a.w_qkv[:64], a.w_qkv[64:96], a.w_qkv[96:]
+        w[f"l{l}.attn.o_proj.weight"] = a.w_o
+    w["l0.attn.q_norm.weight"], w["l0.attn.k_norm.weight"] = blk0.mixer.q_norm, blk0.mixer.k_norm
+    ffns = [(f"l0.moe.expert{e}.", blk0.feed_forward.expert[e]) for e in range(cfg.experts)] + [("l1.mlp.", blk1.feed_forward)]
+    for p, f in ffns:
+        assert f.block == 0                      # widths of 24 and 56: the plain [gates | ups] layout
+        w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"] = f.w_gate_up[:f.F], f.w_gate_up[f.F:], f.w_down
+    w = {k: v.double().cpu().numpy() for k, v in w.items()}
+    rng = np.random.default_rng(1)
+    seqs = {"x": rng.integers(0, cfg.vocab_size, 37).tolist(), "y": rng.integers(0, cfg.vocab_size, 26).tolist()}
+    want, gaps = {}, []
+    for k, v in seqs.items():
+        want[k], g = routed_plain(cfg, w, np.array(v))
+        gaps.append(g)
+    assert min(gaps) > 2e-3, "choose another seed: a token's second and third expert are too close to call"
+
+    def run(plan):
+        got, fed = {k: [] for k in seqs}, {k: 0 for k in seqs}
+        for k in seqs:
+            eng.open_request(k)
+        for step in plan:
+            entries = [StepEntry(k, seqs[k][fed[k]:fed[k] + n], list(range(n))) for k, n in step]
+            out = eng.step(entries).double().cpu().numpy()
+            r = 0
+            for k, n in step:
+                got[k].append(out[r:r + n])
+                r += n
+                fed[k] += n
+        for k in seqs:
+            eng.close_request(k)
+        return {k: np.concatenate(v) for k, v in got.items()}
+
+    whole = run([[("x", 37)], [("y", 26)]])
+    cut = run([[("x", 9), ("y", 2)], [("y", 7)], [("x", 1), ("y", 1)], [("x", 2)], [("x", 25), ("y", 16)]])
+    scale = max(np.abs(v).max() for v in want.values())
+    tol_max = 2e-5 if dtype == torch.float32 else 2e-2
+    for k in seqs:
+        assert np.abs(whole[k] - want[k]).max() <= tol_max * scale
+        assert np.abs(cut[k] - want[k]).max() <= tol_max * scale
