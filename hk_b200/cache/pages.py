@@ -1,6 +1,8 @@
 """Host-side bookkeeping of the paged cache: page pools, block tables, state slots.
 
-Nothing here touches the GPU, so every decision can be tested on the CPU.
+The books themselves are C++ (`csrc/runtime.cpp`, built with the C++ compiler at first use); the classes here
+are views of those objects: tables and lengths are numpy arrays over the native memory, every decision is made
+on the native side.  Nothing here touches the GPU, so every decision can be tested on the CPU.
 
 * A *layer group* is the set of schedule entries whose mixers need the same kind of cache
   (same heads, head size and window).  Each group has a pool of pages and, for every live
@@ -20,10 +22,13 @@ src/cuda/engine.zig:564).
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import numpy as np
+
+from ..csrc import build
 
 
 class CacheError(RuntimeError):
@@ -42,42 +47,82 @@ class ContextFull(CacheError):
     pass
 
 
-class PagePool:
-    """Free list of page ids 0..num_pages-1 with ownership checks."""
+_lib = None
 
-    def __init__(self, num_pages: int):
-        if num_pages < 1:
-            raise ValueError("a pool needs at least one page")
-        self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))   # pop() gives 0 first
-        self._held = np.zeros(num_pages, dtype=bool)
+
+def _runtime() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        lib = build.load("runtime")
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        for name, res, args in [
+            ("hk_pool_create", vp, [ci]), ("hk_pool_destroy", None, [vp]), ("hk_pool_take", ci, [vp]), ("hk_pool_give", ci, [vp, ci]),
+            ("hk_pool_free_count", ci, [vp]), ("hk_pool_num_pages", ci, [vp]), ("hk_pool_held", ctypes.POINTER(ctypes.c_uint8), [vp]),
+            ("hk_pool_error", ctypes.c_char_p, [vp]),
+            ("hk_books_create", vp, [ctypes.POINTER(ci), ci, ci, ci, ci, ci]), ("hk_books_destroy", None, [vp]),
+            ("hk_books_error", ctypes.c_char_p, [vp]), ("hk_books_max_pages", ci, [vp]),
+            ("hk_books_length", ctypes.POINTER(ctypes.c_int64), [vp]), ("hk_books_live", ctypes.POINTER(ctypes.c_uint8), [vp]),
+            ("hk_books_pool", vp, [vp, ci]), ("hk_books_table", ctypes.POINTER(ctypes.c_int32), [vp, ci]),
+            ("hk_books_first_page", ctypes.POINTER(ctypes.c_int32), [vp, ci]), ("hk_books_n_pages", ctypes.POINTER(ctypes.c_int32), [vp, ci]),
+            ("hk_books_open", ci, [vp]), ("hk_books_close", ci, [vp, ci]), ("hk_books_release_passed", ci, [vp, ci]),
+            ("hk_books_pages_to_take", ci, [vp, ci, ci, ctypes.POINTER(ci)]), ("hk_books_pages_passed", ci, [vp, ci, ctypes.POINTER(ci)]), ("hk_books_free_pages", None, [vp, ctypes.POINTER(ci)]),
+            ("hk_books_extend", ci, [vp, ci, ci]), ("hk_books_truncate", ci, [vp, ci, ci]), ("hk_books_audit", ci, [vp]),
+        ]:
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+_ERRORS = {-1: OutOfPages, -2: TooManyRequests, -3: ContextFull, -4: CacheError, -5: ValueError}
+
+
+def _raise(code: int, message: bytes):
+    raise _ERRORS.get(code, CacheError)(message.decode())
+
+
+class PagePool:
+    """Free list of page ids 0..num_pages-1 with ownership checks (a view of a native pool: its own, or the
+    pool of one layer group of a `CacheBooks`)."""
+
+    def __init__(self, num_pages: int, _handle=None, _owner=None):
+        self._rt = _runtime()
+        if _handle is None:
+            if num_pages < 1:
+                raise ValueError("a pool needs at least one page")
+            _handle = self._rt.hk_pool_create(int(num_pages))
+        self._h = ctypes.c_void_p(_handle)
+        self._owner = _owner                 # keeps the books alive; None: this object owns the pool
+        self.num_pages = int(self._rt.hk_pool_num_pages(self._h))
+
+    def __del__(self):
+        if getattr(self, "_owner", None) is None and getattr(self, "_h", None):
+            self._rt.hk_pool_destroy(self._h)
+            self._h = None
 
     @property
     def free_count(self) -> int:
-        return len(self._free)
+        return int(self._rt.hk_pool_free_count(self._h))
 
     def take(self) -> int:
-        if not self._free:
-            raise OutOfPages("no free page")
-        p = self._free.pop()
-        if self._held[p]:
-            raise CacheError(f"page {p} was on the free list while held")
-        self._held[p] = True
-        return p
+        p = self._rt.hk_pool_take(self._h)
+        if p < 0:
+            _raise(p, self._rt.hk_pool_error(self._h))
+        return int(p)
 
     def give(self, page: int) -> None:
-        if not 0 <= page < self.num_pages or not self._held[page]:
-            raise CacheError(f"page {page} is given back but not held")
-        self._held[page] = False
-        self._free.append(page)
+        rc = self._rt.hk_pool_give(self._h, int(page))
+        if rc < 0:
+            _raise(rc, self._rt.hk_pool_error(self._h))
 
     def held(self) -> List[int]:
-        return [int(i) for i in np.nonzero(self._held)[0]]
+        flags = np.ctypeslib.as_array(self._rt.hk_pool_held(self._h), shape=(self.num_pages,))
+        return [int(i) for i in np.nonzero(flags)[0]]
 
 
 @dataclass
 class GroupBooks:
-    """One layer group's pool and block table (host copy)."""
+    """One layer group's pool and block table (views of the native books)."""
     window: Optional[int]
     pool: PagePool
     table: np.ndarray            # int32 [max_requests, max_pages_per_request], -1 = none
@@ -92,142 +137,84 @@ class CacheBooks:
                  max_context: int):
         if page_tokens < 1 or max_requests < 1 or max_context < 1:
             raise ValueError("page_tokens, max_requests and max_context must be positive")
+        if num_pages < 1:
+            raise ValueError("a pool needs at least one page")
+        self._rt = rt = _runtime()
+        windows = list(windows)
+        arr = (ctypes.c_int * max(1, len(windows)))(*[-1 if w is None else int(w) for w in windows])
+        self._h = ctypes.c_void_p(rt.hk_books_create(arr, len(windows), int(page_tokens), int(num_pages), int(max_requests),
+                                                     int(max_context)))
+        if not self._h:
+            raise ValueError("the native books refused these sizes")
         self.page_tokens = page_tokens
         self.max_requests = max_requests
         self.max_context = max_context
-        self.max_pages_per_request = -(-max_context // page_tokens)
+        self.max_pages_per_request = int(rt.hk_books_max_pages(self._h))
+        as_array = np.ctypeslib.as_array
         self.groups: List[GroupBooks] = [
-            GroupBooks(w, PagePool(num_pages),
-                       np.full((max_requests, self.max_pages_per_request), -1, dtype=np.int32),
-                       np.zeros(max_requests, dtype=np.int32), np.zeros(max_requests, dtype=np.int32))
-            for w in windows]
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        self.length = np.zeros(max_requests, dtype=np.int64)    # tokens in the cache, per slot
-        self.live = np.zeros(max_requests, dtype=bool)
+            GroupBooks(w, PagePool(0, _handle=rt.hk_books_pool(self._h, g), _owner=self),
+                       as_array(rt.hk_books_table(self._h, g), shape=(max_requests, self.max_pages_per_request)),
+                       as_array(rt.hk_books_first_page(self._h, g), shape=(max_requests,)),
+                       as_array(rt.hk_books_n_pages(self._h, g), shape=(max_requests,)))
+            for g, w in enumerate(windows)]
+        self.length = as_array(rt.hk_books_length(self._h), shape=(max_requests,))      # tokens in the cache, per slot
+        self.live = as_array(rt.hk_books_live(self._h), shape=(max_requests,)).view(np.bool_)
         self.dirty: set = set()                                 # slots whose table rows changed
+        self._take = (ctypes.c_int * max(1, len(windows)))()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._rt.hk_books_destroy(self._h)
+            self._h = None
+
+    def _check(self, rc: int) -> int:
+        if rc < 0:
+            _raise(rc, self._rt.hk_books_error(self._h))
+        return rc
 
     # -- slots -----------------------------------------------------------------------------
     def open(self) -> int:
-        if not self._free_slots:
-            raise TooManyRequests(f"all {self.max_requests} request slots are in use")
-        s = self._free_slots.pop()
-        self.live[s] = True
-        self.length[s] = 0
-        for g in self.groups:
-            g.first_page[s] = 0
-            g.n_pages[s] = 0
-        return s
+        return self._check(self._rt.hk_books_open(self._h))
 
     def close(self, slot: int) -> None:
-        self._check_live(slot)
-        for g in self.groups:
-            for i in range(int(g.first_page[slot]), int(g.n_pages[slot])):
-                p = int(g.table[slot, i])
-                if p >= 0:
-                    g.pool.give(p)
-            g.table[slot, :int(g.n_pages[slot])] = -1
-            g.first_page[slot] = 0
-            g.n_pages[slot] = 0
-        self.live[slot] = False
-        self.length[slot] = 0
-        self.dirty.add(slot)
-        self._free_slots.append(slot)
-
-    def _check_live(self, slot: int) -> None:
-        if not 0 <= slot < self.max_requests or not self.live[slot]:
-            raise CacheError(f"slot {slot} is not live")
+        self._check(self._rt.hk_books_close(self._h, int(slot)))
+        self.dirty.add(int(slot))
 
     # -- pages -----------------------------------------------------------------------------
-    def _passed(self, g: GroupBooks, slot: int, cur: int) -> List[int]:
-        """Logical pages of a windowed group that no later token can read: the next query sits at
-        position `cur` and reads keys from cur - window + 1 on."""
-        if g.window is None:
-            return []
-        first_needed = max(0, cur - g.window + 1) // self.page_tokens
-        return list(range(int(g.first_page[slot]), min(first_needed, int(g.n_pages[slot]))))
-
     def release_passed(self, slot: int) -> int:
         """Gives back the pages of `slot` that its windows have passed; returns how many."""
-        self._check_live(slot)
-        cur = int(self.length[slot])
-        n = 0
-        for g in self.groups:
-            for i in self._passed(g, slot, cur):
-                g.pool.give(int(g.table[slot, i]))
-                g.table[slot, i] = -1
-                g.first_page[slot] = i + 1
-                n += 1
+        n = self._check(self._rt.hk_books_release_passed(self._h, int(slot)))
         if n:
-            self.dirty.add(slot)
+            self.dirty.add(int(slot))
         return n
+
+    def pages_passed(self, slot: int) -> List[int]:
+        """For each group: the pages `release_passed(slot)` would give back now."""
+        self._check(self._rt.hk_books_pages_passed(self._h, int(slot), self._take))
+        return list(self._take[:len(self.groups)])
 
     def pages_to_take(self, slot: int, n_new: int) -> List[int]:
         """For each group: the pages `extend(slot, n_new)` would take from the pool."""
-        self._check_live(slot)
-        want_pages = -(-(int(self.length[slot]) + n_new) // self.page_tokens)
-        return [max(0, want_pages - int(g.n_pages[slot])) for g in self.groups]
+        self._check(self._rt.hk_books_pages_to_take(self._h, int(slot), int(n_new), self._take))
+        return list(self._take[:len(self.groups)])
 
     def free_pages(self) -> List[int]:
-        return [g.pool.free_count for g in self.groups]
+        self._rt.hk_books_free_pages(self._h, self._take)
+        return list(self._take[:len(self.groups)])
 
     def extend(self, slot: int, n_new: int) -> None:
         """Makes room for `n_new` more tokens of `slot`: gives back pages the window has passed,
         then takes the pages the new positions need.  Takes all of them or none."""
-        self._check_live(slot)
-        if n_new < 1:
-            raise ValueError("extend needs at least one token")
-        cur = int(self.length[slot])
-        if cur + n_new > self.max_context:
-            raise ContextFull(f"request would reach {cur + n_new} tokens; the context holds {self.max_context}")
-        self.release_passed(slot)
-        for g, k in zip(self.groups, self.pages_to_take(slot, n_new)):
-            if k > g.pool.free_count:
-                raise OutOfPages(f"{k} pages needed, {g.pool.free_count} free")
-        want_pages = -(-(cur + n_new) // self.page_tokens)
-        for g in self.groups:
-            for i in range(int(g.n_pages[slot]), want_pages):
-                g.table[slot, i] = g.pool.take()
-                self.dirty.add(slot)
-            g.n_pages[slot] = max(int(g.n_pages[slot]), want_pages)
-        self.length[slot] = cur + n_new
+        if self._check(self._rt.hk_books_extend(self._h, int(slot), int(n_new))):
+            self.dirty.add(int(slot))
 
     def truncate(self, slot: int, keep: int) -> None:
         """Rewinds `slot` to `keep` tokens, giving back the pages above (cf. src/engine/kv.zig:137-151).
         A windowed group cannot rewind below what it already gave back."""
-        self._check_live(slot)
-        if not 0 <= keep <= int(self.length[slot]):
-            raise ValueError("truncate keeps between 0 and the current length")
-        keep_pages = -(-keep // self.page_tokens)
-        for g in self.groups:
-            if g.window is not None and keep > 0 and max(0, keep - g.window) // self.page_tokens < int(g.first_page[slot]):
-                raise CacheError("cannot rewind a windowed cache below pages it has given back")
-            for i in range(max(keep_pages, int(g.first_page[slot])), int(g.n_pages[slot])):
-                g.pool.give(int(g.table[slot, i]))
-                g.table[slot, i] = -1
-            g.n_pages[slot] = min(int(g.n_pages[slot]), keep_pages)
-            g.first_page[slot] = min(int(g.first_page[slot]), keep_pages)
-        self.length[slot] = keep
-        self.dirty.add(slot)
+        self._check(self._rt.hk_books_truncate(self._h, int(slot), int(keep)))
+        self.dirty.add(int(slot))
 
     # -- checks ----------------------------------------------------------------------------
     def audit(self) -> None:
         """Raises if a page is lost, held twice, or free while in a table."""
-        for gi, g in enumerate(self.groups):
-            seen: Dict[int, Tuple[int, int]] = {}
-            for s in range(self.max_requests):
-                row = g.table[s]
-                if not self.live[s]:
-                    if (row >= 0).any():
-                        raise CacheError(f"group {gi}: dead slot {s} still lists pages")
-                    continue
-                for i, p in enumerate(row):
-                    if p < 0:
-                        continue
-                    if int(p) in seen:
-                        raise CacheError(f"group {gi}: page {int(p)} is held twice ({seen[int(p)]} and {(s, i)})")
-                    seen[int(p)] = (s, i)
-            held = set(g.pool.held())
-            if held != set(seen):
-                raise CacheError(f"group {gi}: pool holds {sorted(held - set(seen))} unlisted, tables list {sorted(set(seen) - held)} unheld")
-            if len(held) + g.pool.free_count != g.pool.num_pages:
-                raise CacheError(f"group {gi}: {g.pool.num_pages - len(held) - g.pool.free_count} pages lost")
+        self._check(self._rt.hk_books_audit(self._h))

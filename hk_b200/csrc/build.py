@@ -1,4 +1,5 @@
-"""Builds the CUDA sources of this folder for sm_100a with nvcc and loads them with ctypes.
+"""Builds the CUDA sources of this folder for sm_100a with nvcc (and the host-only C++ runtime with the
+C++ compiler) and loads them with ctypes.
 
 Every library is one `.cu` file compiled alone (no framework headers, so a file takes
 seconds).  Built files live in `_build/` beside the sources, named by a hash of the
@@ -39,7 +40,9 @@ LIBRARIES: Dict[str, str] = {
     "gemm_stream": "gemm_stream.cu",
     "attention_flash": "attention_flash.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
+    "runtime": "runtime.cpp",          # host only: the cache's books (no GPU code, no CUDA headers)
 }
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden"]
 HEADERS: List[str] = ["common.cuh", "attention_noalloc.h"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
@@ -68,6 +71,18 @@ def find_nvcc() -> str:
                      "the CUDA kernels cannot be built and there is no fallback")
 
 
+def find_cxx() -> str:
+    cands = [os.environ.get("HK_B200_CXX"), os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")]
+    for c in cands:
+        if c and (os.path.isfile(c) or shutil.which(c)):
+            return c
+    raise BuildError("no C++ compiler was found (looked at HK_B200_CXX, CXX, g++, c++, clang++); the runtime library cannot be built")
+
+
+def _is_host(name: str) -> bool:
+    return LIBRARIES[name].endswith(".cpp")
+
+
 def build_dir() -> str:
     d = os.environ.get("HK_B200_BUILD_DIR") or os.path.join(HERE, "_build")
     try:
@@ -90,10 +105,10 @@ def _extra_flags() -> List[str]:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for fn in [LIBRARIES[name]] + HEADERS:
+    for fn in [LIBRARIES[name]] + ([] if _is_host(name) else HEADERS):
         with open(os.path.join(HERE, fn), "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
+    h.update(" ".join(HOST_FLAGS if _is_host(name) else NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -108,16 +123,18 @@ def _say(msg: str) -> None:
 def build(name: str, verbose: bool = True) -> str:
     """Compiles library `name` if its built file is absent; returns the file's path."""
     if name not in LIBRARIES:
-        raise BuildError(f"no CUDA library named '{name}'")
+        raise BuildError(f"no library named '{name}'")
     out = library_path(name)
     if os.path.isfile(out):
         return out
-    nvcc = find_nvcc()
     src = os.path.join(HERE, LIBRARIES[name])
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc] + NVCC_FLAGS + _extra_flags() + ["-I", HERE, "-o", tmp, src]
+    if _is_host(name):
+        cmd = [find_cxx()] + HOST_FLAGS + ["-o", tmp, src]
+    else:
+        cmd = [find_nvcc()] + NVCC_FLAGS + _extra_flags() + ["-I", HERE, "-o", tmp, src]
     if verbose:
-        _say(f"compiling {LIBRARIES[name]} for sm_100a ...")
+        _say(f"compiling {LIBRARIES[name]}" + ("" if _is_host(name) else " for sm_100a") + " ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     done = threading.Event()
@@ -138,7 +155,7 @@ def build(name: str, verbose: bool = True) -> str:
             os.unlink(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed on {LIBRARIES[name]} (exit {proc.returncode}):\n{log}")
+        raise BuildError(f"{os.path.basename(cmd[0])} failed on {LIBRARIES[name]} (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
     if verbose:
         _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")

@@ -253,7 +253,7 @@ class Engine:
                     f"request {e.request!r} would reach {int(books.length[slot]) + n} tokens; the context holds {books.max_context}")
             total += n
             # pages the window has passed come back before any are taken
-            passed = [len(books._passed(g, slot, int(books.length[slot]))) for g in books.groups]
+            passed = books.pages_passed(slot)
             for gi, k in enumerate(books.pages_to_take(slot, n)):
                 take[gi] += k - passed[gi]
         if total > self.max_batch_tokens:

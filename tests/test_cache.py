@@ -129,3 +129,13 @@ def test_random_orders_never_lose_or_share_a_page(seed):
         books.close(s)
     books.audit()
     assert all(f == g.pool.num_pages for f, g in zip(books.free_pages(), books.groups))
+
+
+def test_pages_passed_says_what_release_would_give_back():
+    books = CacheBooks([None, 10], page_tokens=4, num_pages=16, max_requests=2, max_context=64)
+    s = books.open()
+    books.extend(s, 30)                      # 8 pages in both groups
+    # the next query sits at position 30 and reads keys from 21 on: logical pages 0..4 of the windowed group are passed
+    assert books.pages_passed(s) == [0, 5]
+    assert books.release_passed(s) == 5 and books.pages_passed(s) == [0, 0]
+    books.audit()
