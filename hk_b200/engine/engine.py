@@ -90,16 +90,23 @@ def _resolve_device(device) -> torch.device:
 
 
 def fill_device_tokens(token_ids: torch.Tensor, on_device) -> None:
-    """Copies device-resident token ids into their rows of `token_ids` (device to device)."""
-    if not on_device:
-        return
-    src = on_device[0][1].tensor
-    if len(on_device) == token_ids.shape[0] and all(d.tensor is src and d.index == r for r, d in on_device) \
-            and src.shape[0] == token_ids.shape[0]:
-        token_ids.copy_(src)                              # the whole batch, in the sampler's order
-        return
-    for r, d in on_device:
-        token_ids[r:r + 1].copy_(d.tensor[d.index:d.index + 1])
+    """Copies device-resident token ids into their rows of `token_ids` (device to device): runs of consecutive
+    rows that take consecutive elements of one tensor go in one copy, repeats of one element in one more."""
+    i, n = 0, len(on_device)
+    while i < n:
+        r0, d0 = on_device[i]
+        j = i + 1
+        while j < n and on_device[j][1].tensor is d0.tensor and on_device[j][0] == r0 + (j - i) \
+                and on_device[j][1].index == d0.index + (j - i):
+            j += 1
+        if j == i + 1:                     # no run: perhaps the same element again and again (rows that fill a batch up)
+            while j < n and on_device[j][1].tensor is d0.tensor and on_device[j][0] == r0 + (j - i) \
+                    and on_device[j][1].index == d0.index:
+                j += 1
+            token_ids[r0:r0 + (j - i)].copy_(d0.tensor[d0.index:d0.index + 1].expand(j - i))
+        else:
+            token_ids[r0:r0 + (j - i)].copy_(d0.tensor[d0.index:d0.index + (j - i)])
+        i = j
 
 
 class PinnedStager:
@@ -313,12 +320,22 @@ class Engine:
             q_lens.append(m)
             r += m
         if self.decode_graphs and n == len(entries) and all(list(e.want) == [0] for e in entries):
-            from .graphs import DecodeGraph
-            g = self._graphs.get(n)
+            from .graphs import DecodeGraph, graph_batch
+            # a graph per batch size would be captured again whenever a request comes or goes; sizes above 8 are
+            # rounded up to the next multiple of 8 and the batch is filled with repeats of its last row (the same
+            # token at the same place: it writes the same key and value again and its logits are dropped)
+            nb = graph_batch(n)
+            if nb > n:
+                meta = np.concatenate([meta, np.repeat(meta[:, -1:], nb - n, axis=1)], axis=1)
+                if on_device and on_device[-1][0] == n - 1:
+                    on_device += [(r, on_device[-1][1]) for r in range(n, nb)]
+                slots = slots + [slots[-1]] * (nb - n)
+                starts = starts + [starts[-1]] * (nb - n)
+            g = self._graphs.get(nb)
             if g is None:
-                g = self._graphs[n] = DecodeGraph(self, n)
+                g = self._graphs[nb] = DecodeGraph(self, nb)
             self.steps_run += 1
-            return g.run(meta, slots, starts, on_device)
+            return g.run(meta, slots, starts, on_device, n)
         meta_dev = self.stager.upload(meta)
         fill_device_tokens(meta_dev[0], on_device)
         ctx = StepContext(self.precision, n, meta_dev[0], meta_dev[1], meta_dev[2], slots, q_starts, q_lens,

@@ -26,6 +26,11 @@ def fill_device_tokens(token_ids, on_device):
     fill(token_ids, on_device)
 
 
+def graph_batch(n: int) -> int:
+    """The batch size of the graph that a decode step of n requests replays: n up to 8, else the next multiple of 8."""
+    return n if n <= 8 else -(-n // 8) * 8
+
+
 class DecodeGraph:
     def __init__(self, engine, batch: int):
         self.engine = engine
@@ -85,9 +90,9 @@ class DecodeGraph:
                            [1] * b, list(starts), plan_builder=builder)
 
     # -- capture and replay ---------------------------------------------------------------------
-    def run(self, meta: np.ndarray, slots, starts, on_device=()) -> torch.Tensor:
+    def run(self, meta: np.ndarray, slots, starts, on_device=(), n_real: int = 0) -> torch.Tensor:
         """meta: int32 [3, B] (token ids, positions, slots); `on_device`: (row, DeviceToken) pairs whose ids are
-        copied in on the device.  Returns the logits [B, vocab]."""
+        copied in on the device.  Returns the logits of the first `n_real` rows (all B by default) [n_real, vocab]."""
         eng = self.engine
         ctx = self._context(slots, starts)
         self._cursor = 3 * self.batch
@@ -121,7 +126,7 @@ class DecodeGraph:
             fill_device_tokens(self.meta[0], on_device)
         self.graph.replay()
         ops.count_launches(self.kernels)
-        return self.logits.clone()      # the static buffer is overwritten by the next replay
+        return self.logits[:n_real or self.batch].clone()      # the static buffer is overwritten by the next replay
 
 
 def model_is_graph_safe(model) -> bool:

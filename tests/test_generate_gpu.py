@@ -83,6 +83,27 @@ def test_run_ahead_decoding_gives_the_same_tokens(tmp_path, dtype):
     assert eng.free_pages() == [eng.cache.books.groups[0].pool.num_pages] * len(eng.cache.books.groups)
 
 
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_decode_graphs_are_shared_by_batch_sizes_that_round_to_the_same(model_b, run_ahead):
+    """Eleven requests of different lengths: the decode batch shrinks from 11 to 1 as they finish.  Sizes above 8
+    replay the graph of the next multiple of 8, filled up with repeats of the last row; the tokens are the plain
+    implementation's."""
+    import hk_b200
+    from hk_b200.api import generate_with_engine
+    d, cfg, w = model_b
+    prompts = helpers.prompts_for("B", np.random.default_rng(12), [3, 9, 4, 17, 6, 5, 11, 8, 2, 7, 10])
+    eng = hk_b200.Engine(d, dtype="float32", max_tokens=11 * 64, max_requests=11, max_context=64)
+    from hk_b200.engine.scheduler import Scheduler
+    from hk_b200.sampling import GREEDY
+    sched = Scheduler(eng, prefill_chunk=64, eos_token_ids=(), run_ahead=run_ahead)
+    ids = [sched.submit(p, 3 + i, GREEDY) for i, p in enumerate(prompts)]
+    done = sched.run()
+    for i, (rid, p) in enumerate(zip(ids, prompts)):
+        assert done[rid].output == plain_greedy(cfg, w, p, 3 + i)
+    assert set(eng._graphs) <= {16, 8, 7, 6, 5, 4, 3, 2, 1} and 16 in eng._graphs
+    assert eng.free_pages() == [eng.cache.num_pages]
+
+
 def test_native_engine_forward_and_rewind(model_b):
     import hk_b200
     d, cfg, w = model_b
