@@ -25,10 +25,10 @@
 #include "common.cuh"
 
 #ifdef HK_TRACE
-// Timing probes for one CTA (block (0, last kv head) of the launch): role r writes clock64() at its n-th probe.
+// Timing probes for one CTA (the first, heaviest work item, kv head 0): role r writes clock64() at its n-th probe.
 __device__ long long hk_trace_buf[4][512];
 __device__ int hk_trace_n[4];
-#define TRACE(role) do { if (trace_on) { int i_ = hk_trace_n[role]; if (i_ < 512) { hk_trace_buf[role][i_] = clock64(); hk_trace_n[role] = i_ + 1; } } } while (0)
+#define TRACE(role) do { if (trace_on) { if (trace_i < 512) { hk_trace_buf[role][trace_i] = clock64(); hk_trace_n[role] = ++trace_i; } } } while (0)
 #else
 #define TRACE(role) do { } while (0)
 #endif
@@ -176,8 +176,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
   const int group = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef HK_TRACE
-  const bool trace_on = blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10);
-  if (threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) { hk_trace_n[0] = hk_trace_n[1] = hk_trace_n[2] = hk_trace_n[3] = 0; }
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10);
+  int trace_i = 0;      // the probe count lives in a register: a probe is one clock read and two stores
+  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) { hk_trace_n[0] = hk_trace_n[1] = hk_trace_n[2] = hk_trace_n[3] = 0; }
 #endif
   const int* bt = block_table + (size_t)it.slot * table_stride;
   const int t_begin = it.kv_lo / TK;
