@@ -100,6 +100,14 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, 
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (128 lanes = rows, 8 columns of two bf16 each per 16 k).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -125,6 +133,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ float ex2(float x) {      // 2^x, one instruction; 2^-inf = 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -143,7 +159,6 @@ struct Smem {
   alignas(1024) uint8_t q[ROWS * HD * 2];
   alignas(1024) uint8_t k[STAGES][TK * HD * 2];
   alignas(1024) uint8_t v[STAGES][TK * HD * 2];
-  alignas(1024) uint8_t p[2][ROWS * TK * 2];     // two P buffers: the softmax of a tile does not wait for the P V product before it
   alignas(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], s_empty[2], p_full[2], pv_done[2];
   float xmax[2][2][ROWS];   // [tile parity][key half][row]: partial row maxima of the two threads of a row
   float xsum[2][ROWS];
@@ -332,12 +347,12 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         if (!mbar_wait(&sm.v_full[st], (uint32_t)((n / STAGES) & 1), abort_flag)) { ok = false; break; }
         TRACE(1);
         tc_fence_after();
-        const uint32_t vs = smem_u32(sm.v[st]), ps = smem_u32(sm.p[n & 1]);
+        const uint32_t vs = smem_u32(sm.v[st]);
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {
-          // P: K-major over the tile's 64 keys (32 bytes per step).  V: MN-major, 16 keys = 16 rows of 128 bytes per step.
-          umma(tmem + O_COL, desc_k_major(ps + (uint32_t)(kk * 32)), desc_mn_major(vs + (uint32_t)kk * 2048u, (uint32_t)(TK * 128)), IDESC_O,
-               (n > 0 || kk > 0) ? 1u : 0u);
+          // P: in tensor memory where the tile's S was (8 columns per step).  V: MN-major, 16 keys = 16 rows of 128 bytes per step.
+          umma_ts(tmem + O_COL, tmem + S_COL[n & 1] + (uint32_t)(kk * 8), desc_mn_major(vs + (uint32_t)kk * 2048u, (uint32_t)(TK * 128)), IDESC_O,
+                  (n > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&sm.v_empty[st]);
         umma_commit(&sm.pv_done[n & 1]);     // tile n's product: barrier n & 1, its completion number n >> 1
@@ -397,29 +412,25 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       const float msafe = mn == -CUDART_INF_F ? 0.f : mn;
       const float corr = move ? exp2f(m - msafe) : 1.0f;  // m = -inf -> 0
       l *= corr;
-      // This tile's P buffer was last read by the P V product of the tile before the last one; O may only be
-      // touched once the product of the last tile has finished, which matters only when the reference moves.
+      // P goes into tensor memory where this tile's S was: both threads of the row have read their halves of S (the
+      // barrier above), and the product that read the P before (two tiles back) ran before this S was written.
+      // O may only be touched once the product of the last tile has finished, which matters only when the
+      // reference moves.  (Two barriers, alternating by tile: a parity wait must never be two completions behind.)
       TRACE(0);
       const bool any_move = __any_sync(0xffffffffu, n > 0 && move);
-      // (Two barriers, alternating by tile: a parity wait must never be two completions behind its barrier.)
-      const int need = any_move ? n - 1 : n - 2;     // the P V product that has to be complete by now
-      if (need >= 0 && !__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[need & 1], (uint32_t)((need >> 1) & 1), abort_flag))) { ok = false; break; }
+      if (any_move && !__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[(n - 1) & 1], (uint32_t)(((n - 1) >> 1) & 1), abort_flag))) { ok = false; break; }
       TRACE(0);
       tc_fence_after();
-      const uint32_t ps = smem_u32(sm.p[n & 1]);
+      uint32_t pw[HK / 2];
 #pragma unroll
-      for (int c = 0; c < HK / 8; ++c) {             // 8 keys = 16 bytes of the row's P
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(su[c * 8 + 2 * e]), scale_log2, -msafe));
-          const float p1 = ex2(fmaf(__uint_as_float(su[c * 8 + 2 * e + 1]), scale_log2, -msafe));
-          l += p0 + p1;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          w[e] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ps + swz(r, half * (HK / 8) + c, ROWS)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+      for (int e = 0; e < HK / 2; ++e) {
+        const float p0 = ex2(fmaf(__uint_as_float(su[2 * e]), scale_log2, -msafe));
+        const float p1 = ex2(fmaf(__uint_as_float(su[2 * e + 1]), scale_log2, -msafe));
+        l += p0 + p1;
+        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        pw[e] = *reinterpret_cast<uint32_t*>(&pk);
       }
+      tmem_st16(lane_addr + S_COL[sb] + (uint32_t)(half * (HK / 2)), pw);
       TRACE(0);
       // tensor-memory loads and stores are warp-wide: if any row of the warp moved its reference, the whole warp
       // goes through its half of the O columns (the others multiply by one)
@@ -433,11 +444,10 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
           tmem_st32(lane_addr + O_COL + (uint32_t)(half * HO + c0), o);
         }
-        tmem_st_wait();
       }
+      tmem_st_wait();                                // P (and O) are in tensor memory before the tensor core is told
       m = mn;
       TRACE(0);
-      fence_async_proxy();                           // P (generic stores) before the tensor core reads it
       TRACE(0);
       tc_fence_before();
       mbar_arrive(&sm.p_full[n & 1]);
