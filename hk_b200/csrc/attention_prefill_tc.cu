@@ -10,12 +10,16 @@
 //   MMA warp (1 lane)  S = Q K^T   : tcgen05.mma 128 x 64 x 16, Q and K K-major from shared memory, S in
 //                                     tensor memory (two S buffers, so the next tile's scores are computed
 //                                     while this tile's softmax runs)
-//                      O += P V    : tcgen05.mma 128 x HD x 16, P K-major from shared memory, V MN-major
+//                      O += P V    : tcgen05.mma 128 x HD x 16, P from tensor memory (two buffers of 32
+//                                     columns beside S and O: it never passes through shared memory), V MN-major
 //                                     (keys are its K dimension) from shared memory, O in tensor memory
 //   softmax warps (8)  two threads per row (half of the tile's keys each): tcgen05.ld of the S row, mask, running
-//                      max and sum in fp32, P = exp2(scale * S - max) written as bf16 to shared memory; the O
-//                      row is rescaled in tensor memory (tcgen05.ld / tcgen05.st) when the reference max has
-//                      to move; at the end O / sum goes out as bf16
+//                      max and sum in fp32, P = exp2(scale * S - max) written as bf16 to tensor memory
+//                      (tcgen05.st); the O row is rescaled in tensor memory (tcgen05.ld / tcgen05.st) when the
+//                      reference max has to move; at the end O / sum goes out as bf16
+//
+// Products into different accumulators are only ordered by their barriers here: a buffer of S, P or O is written
+// again only after a commit has said that the instruction that read it is complete.
 //
 // All hand-offs are mbarriers; every wait is bounded and a time-out makes the CTA set `status`, free its tensor
 // memory and leave without writing.  Reference counterpart: `attention_tc_128`, src/cuda_device.zig:1069-1248
@@ -175,9 +179,10 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             int pages_cap, int* __restrict__ status) {
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = HD / 16;          // MMA k-steps over the head dimension
-  constexpr uint32_t TMEM_COLS = 256;     // two S buffers of 64 columns, O of HD columns
+  constexpr uint32_t TMEM_COLS = 512;     // two S buffers of 64 columns, O of HD columns, two P buffers of 32 (a power of two is allocated)
   constexpr uint32_t S_COL[2] = {0, 64};
   constexpr uint32_t O_COL = 128;
+  constexpr uint32_t P_COL[2] = {256, 288};
   // instruction descriptors: fp32 accumulate, bf16 operands; N at bit 17 (>> 3), M at bit 24 (>> 4); bit 16: B is MN-major
   constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
   constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
@@ -350,8 +355,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         const uint32_t vs = smem_u32(sm.v[st]);
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {
-          // P: in tensor memory where the tile's S was (8 columns per step).  V: MN-major, 16 keys = 16 rows of 128 bytes per step.
-          umma_ts(tmem + O_COL, tmem + S_COL[n & 1] + (uint32_t)(kk * 8), desc_mn_major(vs + (uint32_t)kk * 2048u, (uint32_t)(TK * 128)), IDESC_O,
+          // P: in tensor memory (8 columns per step).  V: MN-major, 16 keys = 16 rows of 128 bytes per step.
+          umma_ts(tmem + O_COL, tmem + P_COL[n & 1] + (uint32_t)(kk * 8), desc_mn_major(vs + (uint32_t)kk * 2048u, (uint32_t)(TK * 128)), IDESC_O,
                   (n > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&sm.v_empty[st]);
@@ -412,13 +417,14 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       const float msafe = mn == -CUDART_INF_F ? 0.f : mn;
       const float corr = move ? exp2f(m - msafe) : 1.0f;  // m = -inf -> 0
       l *= corr;
-      // P goes into tensor memory where this tile's S was: both threads of the row have read their halves of S (the
-      // barrier above), and the product that read the P before (two tiles back) ran before this S was written.
-      // O may only be touched once the product of the last tile has finished, which matters only when the
-      // reference moves.  (Two barriers, alternating by tile: a parity wait must never be two completions behind.)
+      // P goes into one of two buffers in tensor memory: this tile's was last read by the P V product of the tile
+      // before the last one, which has to be complete.  O may only be touched once the product of the last tile has
+      // finished, which matters only when the reference moves.  (Two barriers, alternating by tile: a parity wait
+      // must never be two completions behind its barrier.)
       TRACE(0);
       const bool any_move = __any_sync(0xffffffffu, n > 0 && move);
-      if (any_move && !__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[(n - 1) & 1], (uint32_t)(((n - 1) >> 1) & 1), abort_flag))) { ok = false; break; }
+      const int need = any_move ? n - 1 : n - 2;     // the P V product that has to be complete by now
+      if (need >= 0 && !__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[need & 1], (uint32_t)((need >> 1) & 1), abort_flag))) { ok = false; break; }
       TRACE(0);
       tc_fence_after();
       uint32_t pw[HK / 2];
@@ -430,7 +436,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         pw[e] = *reinterpret_cast<uint32_t*>(&pk);
       }
-      tmem_st16(lane_addr + S_COL[sb] + (uint32_t)(half * (HK / 2)), pw);
+      tmem_st16(lane_addr + P_COL[sb] + (uint32_t)(half * (HK / 2)), pw);
       TRACE(0);
       // tensor-memory loads and stores are warp-wide: if any row of the warp moved its reference, the whole warp
       // goes through its half of the O columns (the others multiply by one)
