@@ -191,8 +191,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
   Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   volatile int* abort_flag = &sm.abort_flag;
 
-  const Item it = items[blockIdx.x];
-  const int g = blockIdx.y;
+  // kv heads are the fast index of the grid: the items come heaviest first, and so do the CTAs of all heads together
+  const Item it = items[blockIdx.y];
+  const int g = blockIdx.x;
   const int group = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef HK_TRACE
@@ -508,7 +509,7 @@ int launch(const void* q, const void* kp, const void* vp, const int* bt, int str
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid((unsigned)n_items, (unsigned)G);
+  dim3 grid((unsigned)G, (unsigned)n_items);
   attention_prefill_tc_kernel<HD><<<grid, NUM_THREADS, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                                  (const Item*)items, (bf16*)out, H, G, pt, window, scale_log2,
                                                                  pages_cap, status);
@@ -525,7 +526,7 @@ HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const voi
                                    int table_stride, const void* items, int n_items, void* out, int H, int G, int hd,
                                    int page_tokens, int window, float scale_log2, int pages_cap, int* status, void* stream) {
   if (n_items <= 0) return 0;
-  if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
+  if (G < 1 || H % G != 0 || (H / G) > ROWS || n_items > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
   if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 128) return launch<128>(q, k_pages, v_pages, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
