@@ -80,8 +80,9 @@ attention_flash_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   bf16* vs = ks + 2 * TILE_N * LD;                          // [2][TILE_N][LD]
   int* tile_pages = reinterpret_cast<int*>(vs + 2 * TILE_N * LD);   // [2][TILE_N]
 
-  const Item it = items[blockIdx.x];
-  const int g = blockIdx.y;
+  // one CTA per (item, kv head), kv heads fastest: prompt items come heaviest first, and so do the CTAs of all heads
+  const Item it = items[blockIdx.x / G];
+  const int g = blockIdx.x % G;
   const int group = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qr = lane >> 2, qt = lane & 3;
@@ -850,7 +851,7 @@ int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, i
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((unsigned)n_items, (unsigned)G);
+  dim3 grid((unsigned)n_items * (unsigned)G);
   attention_flash_kernel<HD, NW><<<grid, NW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                             (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
                                                             scale_log2);

@@ -192,14 +192,14 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
   volatile int* abort_flag = &sm.abort_flag;
 
   // kv heads are the fast index of the grid: the items come heaviest first, and so do the CTAs of all heads together
-  const Item it = items[blockIdx.y];
-  const int g = blockIdx.x;
+  const Item it = items[blockIdx.x / G];
+  const int g = blockIdx.x % G;
   const int group = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef HK_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10);
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10);
   int trace_i = 0;      // the probe count lives in a register: a probe is one clock read and two stores
-  if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) { hk_trace_n[0] = hk_trace_n[1] = hk_trace_n[2] = hk_trace_n[3] = 0; }
+  if (threadIdx.x == 0 && blockIdx.x == 0) { hk_trace_n[0] = hk_trace_n[1] = hk_trace_n[2] = hk_trace_n[3] = 0; }
 #endif
   const int* bt = block_table + (size_t)it.slot * table_stride;
   const int t_begin = it.kv_lo / TK;
@@ -233,13 +233,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
-
-  if (warp >= 9) {
-    // ================================================================= loaders (128 threads)
+  if (warp >= 9) {   // the loaders send for Q at once: it needs nothing of what the others set up
     const int lt = threadIdx.x - 288;
     {   // Q once: row r = (token r / group, head r % group of this kv head's group); rows past the item are zero.
         // A thread copies chunk qc of rows qr0, qr0 + 128 / CPR, ...; token and head advance without divisions.
@@ -260,6 +254,14 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       }
       cp_async_commit();          // the oldest group of this thread; its arrival is signalled inside the tile loop
     }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp >= 9) {
+    // ================================================================= loaders (128 threads)
     bool q_signalled = false;
     // Loader warp w owns stage w and tiles w, w + 4, ...: it can wait for its own copies to land without
     // holding up the other three, so up to four tiles are on their way.  A lane copies chunk `c` of rows r0,
@@ -509,7 +511,7 @@ int launch(const void* q, const void* kp, const void* vp, const int* bt, int str
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid((unsigned)G, (unsigned)n_items);
+  dim3 grid((unsigned)n_items * (unsigned)G);
   attention_prefill_tc_kernel<HD><<<grid, NUM_THREADS, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                                  (const Item*)items, (bf16*)out, H, G, pt, window, scale_log2,
                                                                  pages_cap, status);
@@ -526,7 +528,7 @@ HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const voi
                                    int table_stride, const void* items, int n_items, void* out, int H, int G, int hd,
                                    int page_tokens, int window, float scale_log2, int pages_cap, int* status, void* stream) {
   if (n_items <= 0) return 0;
-  if (G < 1 || H % G != 0 || (H / G) > ROWS || n_items > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
+  if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
   if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 128) return launch<128>(q, k_pages, v_pages, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
