@@ -168,8 +168,9 @@ def cmd_run(args) -> int:
     ctx = g["max_ctx"] or -(-(len(ids) + g["max_tokens"]) // 64) * 64
     try:
         t0 = time.perf_counter()
-        engine = Engine(g["model"], dtype=g["dtype"], max_tokens=ctx, max_requests=1, max_context=ctx,
-                        max_batch_tokens=max(ctx, 1))
+        from .api import SERVING_PAGE_TOKENS
+        engine = Engine(g["model"], dtype=g["dtype"], max_tokens=ctx, page_tokens=SERVING_PAGE_TOKENS, max_requests=1,
+                        max_context=ctx, max_batch_tokens=max(ctx, 1))
         if any(t >= engine.vocab for t in ids):
             print(f"Error: a token id is outside the vocabulary of {engine.vocab}", file=sys.stderr)
             return 1

@@ -23,7 +23,10 @@ import torch
 def _time(fn, reps: int, flush: torch.Tensor):
     times = []
     for i in range(reps + 2):
-        flush.max()           # reading a buffer larger than L2 leaves it full of clean lines that are not the case's
+        if flush is not None:
+            flush.max()       # reading a buffer larger than L2 leaves it full of clean lines that are not the case's
+        else:
+            torch.cuda._sleep(300000)     # L2 left as the run before left it; the GPU idles while the host launches
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -87,6 +90,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--warm", action="store_true", help="do not flush L2 between the timed runs")
     ap.add_argument("--layers", type=int, default=2, help="decode: layers of the model")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--intermediate", type=int, default=12288)
@@ -105,7 +109,7 @@ def main(argv=None) -> int:
         gemm_fast._stream_rw = a.row_warps
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    flush = torch.zeros(64 << 20, dtype=torch.int32, device=dev)      # larger than the 126 MB L2
+    flush = None if a.warm else torch.zeros(64 << 20, dtype=torch.int32, device=dev)      # larger than the 126 MB L2
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     if a.case == "decode":
         return _decode_steps(a, dev)
