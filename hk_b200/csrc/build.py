@@ -47,6 +47,7 @@ HEADERS: List[str] = ["common.cuh", "attention_noalloc.h"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class BuildError(RuntimeError):
@@ -83,19 +84,27 @@ def _is_host(name: str) -> bool:
     return LIBRARIES[name].endswith(".cpp")
 
 
+_build_dir = None
+
+
 def build_dir() -> str:
-    d = os.environ.get("HK_B200_BUILD_DIR") or os.path.join(HERE, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.unlink(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"hk_b200_build_{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    """The folder of the built files: `_build/` beside the sources, or a per-user folder under the temporary
+    directory when that cannot be written (a checkout that belongs to someone else).  Decided once per process."""
+    global _build_dir
+    with _dir_lock:
+        if _build_dir is None:
+            d = os.environ.get("HK_B200_BUILD_DIR") or os.path.join(HERE, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                probe = os.path.join(d, f".w{os.getpid()}.{threading.get_ident()}")
+                with open(probe, "w"):
+                    pass
+                os.unlink(probe)
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"hk_b200_build_{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+            _build_dir = d
+        return _build_dir
 
 
 def _extra_flags() -> List[str]:
