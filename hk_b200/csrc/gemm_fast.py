@@ -93,8 +93,9 @@ def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
 
 
 STREAM_M = 32         # the most rows the persistent streaming kernel takes
-STREAM_M_AUTO = 8     # up to here it is chosen
-STREAM_MIN_WEIGHTS = 40 << 20    # ... for weights of at least this many elements (see `stream_row_warps`)
+STREAM_M_AUTO = 8     # up to here it is chosen ...
+STREAM_MIN_WEIGHTS = 40 << 20    # ... for weights of at least this many elements (see `stream_wanted`)
+STREAM_M_AUTO_WIDE = 16          # ... and up to here for weights of any size
 _stream_rw = 0        # tests and tuning runs may pin the consumer warps across a tile's rows (8, 4, 2, 1)
 _stream_ctas = 0      # tests may run fewer CTAs than SMs to move the places where CTAs hand a tile over
 _stream_scratch = {}
@@ -130,10 +131,13 @@ def stream_row_warps(N: int, sms: int) -> int:
 
 
 def stream_wanted(M: int, N: int, K: int) -> bool:
-    """The streaming kernel pays about two microseconds to fill its ring and to hand shared tiles over; measured
-    on the 8B model's decode products it wins from about 80 MB of weights up (gate/up, down, output head) and
-    loses to the small-M kernel below (q/k/v, o)."""
-    return M <= STREAM_M_AUTO and N * K >= STREAM_MIN_WEIGHTS and K % 64 == 0
+    """The streaming kernel pays about two microseconds to fill its ring and to hand shared tiles over.  Measured
+    on the 8B model's decode products: up to 8 rows it wins from about 80 MB of weights up (gate/up, down, output
+    head) and loses to the small-M kernel below (q/k/v, o); from 9 to 16 rows it wins at every shape, against the
+    small-M kernel and against the tcgen05 kernel with K slices; from 17 rows on the tcgen05 kernel is ahead."""
+    if K % 64:
+        return False
+    return (M <= STREAM_M_AUTO and N * K >= STREAM_MIN_WEIGHTS) or STREAM_M_AUTO < M <= STREAM_M_AUTO_WIDE
 
 
 def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
