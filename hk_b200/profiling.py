@@ -90,6 +90,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits per request and kv head (default: as the decode graphs choose)")
     ap.add_argument("--warm", action="store_true", help="do not flush L2 between the timed runs")
     ap.add_argument("--layers", type=int, default=2, help="decode: layers of the model")
     ap.add_argument("--hidden", type=int, default=4096)
@@ -138,7 +139,7 @@ def main(argv=None) -> int:
             q = torch.randn(n, H * hd, device=dev).to(torch.bfloat16)
             pos = torch.full((n,), a.ctx - 1, dtype=torch.int32, device=dev)
             slot = torch.arange(n, dtype=torch.int32, device=dev)
-            splits = max(1, min(32, 2 * sms // (n * G)))
+            splits = a.splits or max(1, min(16, 2 * sms // (n * G)))
             plan = attention_fast.build_plan(list(range(n)), list(range(n)), [1] * n, [a.ctx - 1] * n, n, 0, H, G, sms, upload,
                                              fixed_splits=splits)
             nbytes = 2.0 * 2 * n * a.ctx * G * hd
