@@ -159,13 +159,28 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), _stream()), "swiglu")
 
 
+def _as_weights(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """A product runs in its weights' type: where a matrix is kept in 32-bit although the engine computes in
+    bfloat16 (its file stored it so), the activations are widened for that product (and narrowed for the next)."""
+    if a.dtype == w.dtype:
+        return a
+    if w.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"weights must be float32 or bfloat16, not {w.dtype}")
+    return a.to(w.dtype)
+
+
 def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, block: int) -> None:
     """out[M, F] = silu(gate) * up of a @ w_paired^T, w_paired [2F, K] laid out [block gates | block ups |
     ...] (block = 0: [F gates | F ups]).  Fused into the tensor-core product's epilogue when that takes the
     shape, else a product to float32 followed by the swiglu kernel."""
     _need(a, "a", dims=2)
-    _need(w_paired, "w", a.dtype, 2)
+    _need(w_paired, "w", dims=2)
     _need(out, "out", a.dtype, 2)
+    if w_paired.dtype != a.dtype:              # weights kept in 32-bit on the bfloat16 path: this product runs in 32-bit
+        wide = torch.empty(out.shape, dtype=w_paired.dtype, device=out.device)
+        gemm_swiglu(_as_weights(a, w_paired), w_paired, wide, block)
+        out.copy_(wide)
+        return
     M, F = out.shape
     if a.shape[0] != M or w_paired.shape != (2 * F, a.shape[1]):
         raise KernelError("gemm_swiglu: shapes do not fit")
@@ -230,8 +245,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
     """out[M, N] (float32) = a[M, K] @ w[N, K]^T (+ out when `accumulate`).
     a and w share a type: float32 (plain FMA) or bfloat16 (fp32 accumulation)."""
     _need(a, "a", dims=2)
-    _need(w, "w", a.dtype, 2)
+    _need(w, "w", dims=2)
     _need(out, "out", torch.float32, 2)
+    a = _as_weights(a, w)
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or tuple(out.shape) != (M, N):

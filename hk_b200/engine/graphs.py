@@ -12,6 +12,7 @@ device tensors alone) are captured.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List
 
 import numpy as np
@@ -108,9 +109,18 @@ class DecodeGraph:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(graph):
-                x = eng.model.forward(ctx, eng.cache.layers)
-                self.logits = eng.model.head.forward(x, self.rows, self.batch, ctx)
+            # No cyclic garbage collection while the stream is capturing: it could finalise another engine's graphs,
+            # and freeing those is an operation that a capture in progress does not permit.
+            gc_was_on = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    x = eng.model.forward(ctx, eng.cache.layers)
+                    self.logits = eng.model.head.forward(x, self.rows, self.batch, ctx)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.kernels = ops.launch_count() - before      # kernel nodes of the graph
             ops.count_launches(-self.kernels)               # capturing launched nothing
             self.graph = graph

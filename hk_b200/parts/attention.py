@@ -68,8 +68,9 @@ class GQAAttention(Part):
 
     def own_bind(self, tensors, precision: Precision) -> None:
         p = self.prefix
-        self.w_qkv = torch.cat([tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"],
-                                tensors[p + "v_proj.weight"]], dim=0).contiguous()
+        qkv = [tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"], tensors[p + "v_proj.weight"]]
+        wide = torch.float32 if any(t.dtype == torch.float32 for t in qkv) else qkv[0].dtype    # one kept in 32-bit: all are
+        self.w_qkv = torch.cat([t.to(wide) for t in qkv], dim=0).contiguous()
         self.w_o = tensors[p + "o_proj.weight"]
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[p + "q_norm.weight"]

@@ -35,7 +35,9 @@ class SwiGLUFeedForward(Part):
         # of the tensor-core product holds both halves and SwiGLU runs in its epilogue
         # (cf. the interleaved gate/up of shaders/swiglu_pair.comp:2).  Otherwise [all gates | all ups].
         from ..csrc import gemm_fast
-        if precision.compute == torch.bfloat16 and self.F % gemm_fast.PAIR == 0:
+        if gate.dtype != up.dtype:                  # one of them kept in 32-bit: both are
+            gate, up = gate.float(), up.float()
+        if gate.dtype == torch.bfloat16 and self.F % gemm_fast.PAIR == 0:
             self.block = gemm_fast.PAIR
             self.w_gate_up = gemm_fast.pair_gate_up(gate, up)
         else:

@@ -78,7 +78,10 @@ def load_tensors(model_dir: str, specs: Dict[str, ParamSpec], precision: Precisi
     for name, spec in specs.items():
         if name in where:
             t = where[name].tensor(name)
-            out[name] = t.to(device=precision.device, dtype=precision.working_dtype(spec.kind)).contiguous()
+            dtype = precision.working_dtype(spec.kind)
+            if t.dtype == torch.float32 and dtype == torch.bfloat16:
+                dtype = torch.float32          # a tensor stored in 32-bit stays so: the file says it needs them
+            out[name] = t.to(device=precision.device, dtype=dtype).contiguous()
     for f in files:
         f.close()
     return out

@@ -104,6 +104,40 @@ def test_decode_graphs_are_shared_by_batch_sizes_that_round_to_the_same(model_b,
     assert eng.free_pages() == [eng.cache.num_pages]
 
 
+def test_matrices_stored_in_32_bit_run_in_32_bit_on_the_bfloat16_path(tmp_path):
+    """A bfloat16 model folder in which a few matrices (and the embedding) are stored as float32 with values that
+    bfloat16 cannot hold: the engine keeps them so, runs their products in 32-bit, and the logits follow the plain
+    implementation of exactly the stored values, whole and cut."""
+    from hk_b200.engine import Engine, StepEntry
+    from hk_b200.weights import load_tensors
+    from hk_b200.weights.safetensors_io import save_file
+    d = helpers.make_model_dir(tmp_path, "A", torch.bfloat16)
+    path = os.path.join(d, "model.safetensors")
+    stored = {k: torch.from_numpy(v).float() for k, v in helpers.read_safetensors(path).items()}
+    names32 = ["model.embed_tokens.weight", "model.layers.0.self_attn.k_proj.weight", "model.layers.0.mlp.gate_proj.weight",
+               "model.layers.1.self_attn.o_proj.weight", "model.layers.1.mlp.down_proj.weight"]
+    g = torch.Generator().manual_seed(4)
+    out = {k: (v + 2e-4 * torch.randn(v.shape, generator=g)).float() if k in names32 else v.to(torch.bfloat16) for k, v in stored.items()}
+    save_file(out, path)
+    cfg, w = helpers.load_plain(d)
+    eng = Engine(d, dtype="bfloat16", max_tokens=128, page_tokens=16, max_requests=2)
+    blk0, blk1 = eng.model.layers[0], eng.model.layers[1]
+    assert eng.model.embedding.table.dtype == torch.float32
+    assert blk0.mixer.w_qkv.dtype == torch.float32 and blk0.mixer.w_o.dtype == torch.bfloat16
+    assert blk0.feed_forward.w_gate_up.dtype == torch.float32 and blk0.feed_forward.w_down.dtype == torch.bfloat16
+    assert blk1.mixer.w_qkv.dtype == torch.bfloat16 and blk1.mixer.w_o.dtype == torch.float32
+    assert blk1.feed_forward.w_down.dtype == torch.float32
+    ids = helpers.prompts_for("A", np.random.default_rng(3), [45])[0]
+    ref = P.forward(cfg, w, ids)
+    scale = np.abs(ref).max()
+    eng.open_request("w")
+    whole = eng.step([StepEntry("w", ids, list(range(45)))]).double().cpu().numpy()
+    eng.open_request("c")
+    parts = [eng.step([StepEntry("c", ids[a:b], list(range(b - a)))]).double().cpu().numpy() for a, b in ((0, 17), (17, 19), (19, 44), (44, 45))]
+    assert np.abs(whole - ref).max() <= 2e-2 * scale
+    assert np.abs(np.concatenate(parts) - ref).max() <= 2e-2 * scale
+
+
 def test_native_engine_forward_and_rewind(model_b):
     import hk_b200
     d, cfg, w = model_b

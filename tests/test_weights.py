@@ -135,3 +135,26 @@ def test_sharded_folder_follows_the_index(tmp_path):
         json.dump({"weight_map": wm}, fh)
     t = load_tensors(d, specs_of(helpers.TINY_A), cpu(torch.float32))
     assert torch.equal(t["model.embed_tokens.weight"], tensors["model.embed_tokens.weight"])
+
+
+def test_a_tensor_stored_in_32_bit_stays_so_on_the_bfloat16_path(tmp_path):
+    from hk_b200.weights.safetensors_io import save_file
+    d = helpers.make_model_dir(tmp_path, "A", torch.bfloat16)
+    path = os.path.join(d, "model.safetensors")
+    t0 = load_tensors(d, specs_of(helpers.TINY_A), cpu(torch.float32))      # everything, widened
+    names32 = ["model.layers.0.self_attn.q_proj.weight", "model.layers.1.mlp.down_proj.weight", "model.norm.weight"]
+    out = {}
+    g = torch.Generator().manual_seed(3)
+    for k, v in t0.items():
+        if k in names32:
+            out[k] = (v + 1e-4 * torch.randn(v.shape, generator=g)).float()      # not representable in bfloat16
+        else:
+            out[k] = v.to(torch.bfloat16)
+    save_file(out, path)
+    t = load_tensors(d, specs_of(helpers.TINY_A), cpu(torch.bfloat16))
+    for k, v in t.items():
+        if k in names32 or k.endswith("norm.weight") or k.endswith("layernorm.weight"):
+            assert v.dtype == torch.float32, k
+        else:
+            assert v.dtype == torch.bfloat16, k
+    assert torch.equal(t[names32[0]], out[names32[0]])
