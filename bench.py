@@ -63,16 +63,18 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append([c.strip() for c in line.split(",")])
+            self.samples.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def stop(self, window=None):
+        """Ends the sampling; the summary counts the samples taken inside `window` = (start, end) in time.time()
+        seconds (the sampler is started earlier: nvidia-smi takes a moment to print its first line)."""
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -80,7 +82,9 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
         mhz, mx, reasons = [], 0, set()
-        for s in self.samples:
+        for t, s in self.samples:
+            if window is not None and not window[0] <= t <= window[1]:
+                continue
             try:
                 mhz.append(int(s[0]))
                 mx = max(mx, int(s[1]))
@@ -166,6 +170,8 @@ def run(args):
     # ---- decode at batch B: every request holds PROMPT tokens, then W + K single-token steps ----
     def decode_point(batch, steps, warmup, clocks=None):
         ids = [f"d{i}" for i in range(batch)]
+        if clocks is not None:
+            clocks.start()
         for r in ids:
             engine.open_request(r)
         # fill the contexts: real prefill steps, several requests per step
@@ -175,32 +181,33 @@ def run(args):
         toks = rng.integers(0, vocab, (warmup + steps, batch))
         out = torch.empty(batch, dtype=torch.int32, device=engine.device)
         launches0 = None
+        window = [0.0, 0.0]
         a, b = ev(), ev()
         for s in range(warmup + steps):
             if s == warmup:
                 torch.cuda.synchronize()
-                if clocks is not None:
-                    clocks.start()
+                window[0] = time.time()
                 launches0 = ops.launch_count()
                 a.record()
             logits = engine.step([StepEntry(r, [int(toks[s, i])], [0]) for i, r in enumerate(ids)])
             ops.argmax(logits, out)
         b.record()
         torch.cuda.synchronize()
+        window[1] = time.time()
         ms = a.elapsed_time(b) / steps
         launches = ops.launch_count() - launches0
         for r in ids:
             engine.close_request(r)
-        return ms, launches
+        return ms, launches, tuple(window)
 
     clocks = ClockSampler()
-    main_ms, launches = decode_point(8, args.steps, args.warmup, clocks)
-    clock_info = clocks.stop()
+    main_ms, launches, timed = decode_point(8, args.steps, args.warmup, clocks)
+    clock_info = clocks.stop(timed)
     points = {}
     for bsz in batches:
         if bsz == 8:
             continue
-        ms, _ = decode_point(bsz, max(4, args.steps // 2), max(3, args.warmup))
+        ms, _, _ = decode_point(bsz, max(4, args.steps // 2), max(3, args.warmup))
         points[f"decode_b{bsz}"] = bsz / ms * 1e3
 
     # ---- end to end through the Python entry point (batch 8) ----
