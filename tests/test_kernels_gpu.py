@@ -157,6 +157,37 @@ def test_qk_norm_rope_kv_write(dtype, H, G, hd, pt, rot, norm):
     assert torch.equal(q2, q_out) and not kp2.any() and not vp2.any()
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,hd,pt,rot,norm,ntok", [(32, 8, 128, 16, 128, True, 700), (7, 1, 64, 8, 32, True, 1843), (9, 3, 48, 16, 48, False, 1097)])
+def test_qk_norm_rope_kv_write_many_tokens(dtype, H, G, hd, pt, rot, norm, ntok):
+    # a prompt's worth of (token, head) items: item counts that are no multiple of a block, tokens of two requests at
+    # places that straddle pages
+    rng = np.random.default_rng(H * hd + pt + ntok)
+    n0 = ntok // 3
+    lens = [n0 + 5, ntok - n0 + 11]
+    k_pages, v_pages, bt, _, _ = make_paged(rng, 2, lens, G, hd, pt, dtype)
+    k_pages.zero_()
+    v_pages.zero_()
+    slot = torch.tensor([0] * n0 + [1] * (ntok - n0), dtype=torch.int32)
+    pos = torch.tensor(list(range(5, 5 + n0)) + list(range(11, 11 + ntok - n0)), dtype=torch.int32)
+    qkv = torch.from_numpy(rng.standard_normal((ntok, (H + 2 * G) * hd))).float() * 2
+    qw = (1 + 0.2 * torch.from_numpy(rng.standard_normal(hd))).float() if norm else None
+    kw = (1 + 0.2 * torch.from_numpy(rng.standard_normal(hd))).float() if norm else None
+    ang = torch.arange(max(lens) + 1, dtype=torch.float64)[:, None] * torch.from_numpy(rng.uniform(0.001, 1.0, rot // 2))[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    q_out = torch.empty(ntok, H * hd, dtype=dtype, device=DEV)
+    kp, vp = k_pages.to(DEV), v_pages.to(DEV)
+    d = lambda t: None if t is None else t.to(DEV)
+    ops().qk_norm_rope_kv_write(qkv.to(DEV), q_out, d(qw), d(kw), 1e-6, d(cos), d(sin), rot, pos.to(DEV), slot.to(DEV), bt.to(DEV),
+                                kp, vp, H, G, hd, pt)
+    q, k, v = ref_ops.qk_norm_rope(qkv, qw, kw, 1e-6, cos, sin, rot, pos, H, G, hd)
+    close(q_out, q.reshape(ntok, H * hd), dtype)
+    rk, rv = torch.zeros_like(k_pages, dtype=torch.float64), torch.zeros_like(v_pages, dtype=torch.float64)
+    ref_ops.write_pages(k, v, rk, rv, bt, slot, pos, pt)
+    close(kp, rk, dtype)
+    close(vp, rv, dtype)
+
+
 def test_rotation_reference_fact():
     # src/engine/ops.zig:236-252: 90 degrees in the half-split pairing: [1,0,0,1] -> [0,-1,1,0]
     qkv = torch.tensor([[1.0, 0, 0, 1] + [0.0] * 8], device=DEV)
