@@ -138,6 +138,39 @@ def test_matrices_stored_in_32_bit_run_in_32_bit_on_the_bfloat16_path(tmp_path):
     assert np.abs(np.concatenate(parts) - ref).max() <= 2e-2 * scale
 
 
+@pytest.mark.parametrize("which,page_tokens,max_tokens", [("C", 16, 256), ("D", 16, 384), ("B", 8, 104)])
+def test_scheduler_under_pressure_follows_the_plain_implementation(tmp_path, which, page_tokens, max_tokens):
+    """Twelve requests arrive while others run, over three slots and a pool so small that requests wait, prompt
+    portions are shortened, pages are reused and the newest request is preempted and recomputed; windowed
+    configurations give pages back as they go.  Every request's greedy tokens are the plain implementation's."""
+    from hk_b200.engine import Engine
+    from hk_b200.engine.scheduler import Scheduler
+    from hk_b200.sampling import GREEDY
+    d = helpers.make_model_dir(tmp_path, which, torch.float32)
+    cfg, w = helpers.load_plain(d)
+    rng = np.random.default_rng(21)
+    lengths = [int(x) for x in rng.integers(3, 70, 12)]
+    news = [int(x) for x in rng.integers(2, 14, 12)]
+    prompts = helpers.prompts_for(which, rng, lengths)
+    eng = Engine(d, dtype="float32", max_tokens=max_tokens, page_tokens=page_tokens, max_requests=3, max_context=96, max_batch_tokens=40)
+    sched = Scheduler(eng, prefill_chunk=24, eos_token_ids=(), run_ahead=True)
+    ids, k = [], 0
+    for step in range(2000):
+        if k < 12 and step % 3 == 0:
+            ids.append(sched.submit(prompts[k], news[k], GREEDY))
+            k += 1
+        if not sched.has_work() and k == 12:
+            break
+        sched.step()
+        eng.cache.books.audit()
+    assert k == 12 and not sched.has_work()
+    for rid, p, n in zip(ids, prompts, news):
+        assert sched.finished[rid].output == plain_greedy(cfg, w, p, n), f"request {rid}"
+    assert eng.free_pages() == [eng.cache.num_pages] * len(eng.cache.books.groups)
+    if which == "B":
+        assert sched.stats.preemptions >= 1
+
+
 def test_native_engine_forward_and_rewind(model_b):
     import hk_b200
     d, cfg, w = model_b
