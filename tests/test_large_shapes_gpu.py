@@ -47,3 +47,33 @@ def test_bfloat16_engine_follows_the_float32_engine_at_serving_sizes():
     top2 = a.topk(2, dim=1).values
     clear = (top2[:, 0] - top2[:, 1]) / scale > 2e-2
     assert torch.equal(a.argmax(1)[clear], b.argmax(1)[clear])
+
+
+def test_decode_batch_of_twenty_at_serving_sizes():
+    """Twenty requests decoding together: the graph of 24 rows (filled up with repeats), tcgen05 products with K
+    slices for 24 rows, decode attention without key splits; against the float32 engine."""
+    from hk_b200.config import config_from_dict
+    from hk_b200.engine import Engine, StepEntry
+    cfg = config_from_dict(SHAPE)
+    rng = np.random.default_rng(1)
+    v = SHAPE["vocab_size"]
+    prompts = [rng.integers(0, v, int(n)).tolist() for n in rng.integers(90, 330, 20)]
+    outs = {}
+    for dt in ("float32", "bfloat16"):
+        e = Engine(config=cfg, random_seed=9, dtype=dt, max_tokens=20 * 384, page_tokens=64, max_requests=20, max_context=384,
+                   max_batch_tokens=4096)
+        for i in range(20):
+            e.open_request(i)
+        for lo in (0, 10):
+            e.step([StepEntry(i, prompts[i], []) for i in range(lo, lo + 10)])
+        res = [e.step([StepEntry(i, [7 + s + i], [0]) for i in range(20)]).float().cpu() for s in range(3)]
+        outs[dt] = torch.cat(res)
+        if dt == "bfloat16":
+            assert 24 in e._graphs
+            from hk_b200.csrc import gemm_fast
+            gemm_fast.check_status(e.device)
+        del e
+        torch.cuda.empty_cache()
+    a, b = outs["float32"], outs["bfloat16"]
+    scale = a.abs().max().item()
+    assert ((a - b).abs().max(dim=1).values / scale).max().item() <= 2e-2
