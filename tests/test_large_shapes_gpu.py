@@ -77,3 +77,43 @@ def test_decode_batch_of_twenty_at_serving_sizes():
     a, b = outs["float32"], outs["bfloat16"]
     scale = a.abs().max().item()
     assert ((a - b).abs().max(dim=1).values / scale).max().item() <= 2e-2
+
+
+WIDER = {
+    # one layer each of the two larger serving shapes: a hidden width that is no power of two, 40 and 64 query heads
+    # (query width equal to and larger than the hidden width), feed-forward widths of 17,408 and 25,600
+    "hidden5120_heads40": dict(hidden_size=5120, num_attention_heads=40, intermediate_size=17408, vocab_size=20011),
+    "hidden5120_heads64": dict(hidden_size=5120, num_attention_heads=64, intermediate_size=25600, vocab_size=16001),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WIDER))
+def test_wider_serving_shapes(name):
+    """Prompt steps (one of more than a thousand rows, one mixed with a decoded token) and replayed decode graphs at
+    the layer sizes of the larger models of the family; the bfloat16 engine against the float32 engine."""
+    from hk_b200.config import config_from_dict
+    from hk_b200.engine import Engine, StepEntry
+    cfg = config_from_dict(dict(SHAPE, num_hidden_layers=1, max_position_embeddings=2048, **WIDER[name]))
+    rng = np.random.default_rng(2)
+    v = cfg.vocab_size
+    prompts = {"a": rng.integers(0, v, 1100).tolist(), "b": rng.integers(0, v, 150).tolist(), "c": rng.integers(0, v, 77).tolist()}
+    outs = {}
+    for dt in ("float32", "bfloat16"):
+        e = Engine(config=cfg, random_seed=11, dtype=dt, max_tokens=2048, page_tokens=64, max_requests=3, max_context=1280,
+                   max_batch_tokens=2048)
+        for k in prompts:
+            e.open_request(k)
+        res = [e.step([StepEntry("a", prompts["a"], [0, 1099])]).float().cpu(),
+               e.step([StepEntry("b", prompts["b"], [149]), StepEntry("a", [3], [0]), StepEntry("c", prompts["c"], [76])]).float().cpu()]
+        for s in range(4):
+            res.append(e.step([StepEntry(k, [50 + s], [0]) for k in prompts]).float().cpu())
+        outs[dt] = torch.cat(res)
+        if dt == "bfloat16":
+            assert 3 in e._graphs
+            from hk_b200.csrc import gemm_fast
+            gemm_fast.check_status(e.device)
+        del e
+        torch.cuda.empty_cache()
+    a, b = outs["float32"], outs["bfloat16"]
+    scale = a.abs().max().item()
+    assert ((a - b).abs().max(dim=1).values / scale).max().item() <= 2e-2
