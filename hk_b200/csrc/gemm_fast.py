@@ -76,12 +76,18 @@ def cluster_size(M: int, N: int, rt: int, device) -> int:
     return _cs_override or 1
 
 
+_tc_bn = 0            # tests and tuning runs may pin the tile width (128 or 256) ...
+_tc_splits = 0        # ... and the number of K slices of the tcgen05 kernel
+
+
 def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
     """Tile width and number of K slices for the tcgen05 kernel.  Wide tiles when they still fill half
     the SMs; with fewer output tiles than SMs (few rows: decode batches, narrow outputs) K is cut into
     slices so that every SM streams a share of the weights.  (A finer cost model that also weighed wave
     tails chose more slices and measured slower: the second kernel that adds the slices has a fixed cost.)"""
     m_tiles = -(-M // 128)
+    if bn == 0 and _tc_bn:
+        bn = _tc_bn
     if bn == 0:
         bn = 256 if N >= 256 and m_tiles * -(-N // 256) >= sms // 2 else 128
     tiles = m_tiles * -(-N // bn)
@@ -89,6 +95,8 @@ def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
     splits = 1
     if tiles < sms:
         splits = max(1, min(sms // tiles, k_blocks // 8))
+    if _tc_splits:
+        splits = min(_tc_splits, k_blocks)
     return bn, splits
 
 

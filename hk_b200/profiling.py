@@ -90,7 +90,8 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
-    ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits per request and kv head (default: as the decode graphs choose)")
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits per request and kv head (default: as the decode graphs choose); gemm_tc: K slices")
+    ap.add_argument("--bn", type=int, default=0, help="gemm_tc: pin the tile width (128 or 256)")
     ap.add_argument("--warm", action="store_true", help="do not flush L2 between the timed runs")
     ap.add_argument("--layers", type=int, default=2, help="decode: layers of the model")
     ap.add_argument("--hidden", type=int, default=4096)
@@ -106,6 +107,8 @@ def main(argv=None) -> int:
     gemm_fast._rt_override = a.row_tiles
     gemm_fast._cs_override = a.cluster
     gemm_fast._stream_ctas = a.ctas
+    if a.case == "gemm_tc":
+        gemm_fast._tc_bn, gemm_fast._tc_splits = a.bn, a.splits
     if a.row_warps:
         gemm_fast._stream_rw = a.row_warps
     dev = torch.device("cuda", 0)
