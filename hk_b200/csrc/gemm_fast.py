@@ -1,10 +1,13 @@
 """Choice among the bfloat16 tensor-core matrix products.
 
-  * up to 8 rows (small decode batches): the weight-streaming mma.sync kernel (`gemm_smallm.cu`);
-  * more rows (larger decode batches, prefill, mixed batches): the persistent tcgen05 kernel
-    (`gemm_tc.cu`), cutting K into slices when the output has fewer tiles than the GPU has SMs.
-The choice depends on the shape alone.  Shapes both refuse (K not a multiple of 8, unaligned
-operands) go to the generic kernel.
+  * up to 8 rows (small decode batches): the persistent TMA-ring streaming kernel (`gemm_stream.cu`) for large
+    weights (gate/up, down, the output head), the weight-streaming mma.sync kernel (`gemm_smallm.cu`) for the
+    smaller ones (q/k/v, o);
+  * 9 to 16 rows: the streaming kernel at every shape;
+  * more rows (larger decode batches, prefill, mixed batches): the persistent tcgen05 kernel (`gemm_tc.cu`),
+    cutting K into slices when the output has fewer tiles than the GPU has SMs.
+The choice depends on the shape alone, so a token's logits do not depend on what else a process ran before.
+Shapes all of them refuse (K not a multiple of 8, unaligned operands) go to the generic kernel.
 """
 from __future__ import annotations
 
