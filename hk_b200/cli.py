@@ -28,6 +28,11 @@ USAGE = """Usage: hk run <model folder> [token ids | -p IDS] [options]
       --backend B       auto | cuda; cpu and vulkan are refused (this engine is CUDA only)
       --dtype D         bfloat16 | float32 (default bfloat16)
       --max-ctx N       context length to provide (default: prompt + max tokens, rounded up to 64)
+      --prompt-len N    instead of a prompt: N token ids drawn uniformly from the vocabulary with --seed
+      --page-tokens N   tokens per cache page (default 64)
+
+       hk random <config.json> <new model folder> [--seed N] [--dtype D] [--std S]
+                        writes config.json and model.safetensors with seeded random weights
 """
 
 
@@ -83,7 +88,7 @@ def parse_ids(text: str):
 def parse_run_args(args):
     """Returns a dict of settings; raises BadUsage on anything unknown or malformed."""
     g = dict(model=None, prompt=None, max_tokens=128, temperature=0.8, top_k=40, top_p=0.95, min_p=0.05,
-             repeat_penalty=1.0, seed=0, dtype="bfloat16", max_ctx=None)
+             repeat_penalty=1.0, seed=0, dtype="bfloat16", max_ctx=None, prompt_len=None, page_tokens=None)
     i = 0
     while i < len(args):
         flag = args[i]
@@ -136,6 +141,12 @@ def parse_run_args(args):
         elif flag == "--max-ctx":
             g["max_ctx"] = _uint(args, i, flag, 1)
             i += 2
+        elif flag == "--prompt-len":
+            g["prompt_len"] = _uint(args, i, flag, 1)
+            i += 2
+        elif flag == "--page-tokens":
+            g["page_tokens"] = _uint(args, i, flag, 1)
+            i += 2
         elif flag.startswith("-") and len(flag) > 1 and not flag[1:].replace(",", "").replace(" ", "").isdigit():
             _fail(f"Error: unknown argument '{flag}'")
         elif g["model"] is None:
@@ -148,9 +159,11 @@ def parse_run_args(args):
             i += 1
     if g["model"] is None:
         _fail("Error: no model folder was given")
-    if g["prompt"] is None:
+    if g["prompt"] is not None and g["prompt_len"] is not None:
+        _fail("Error: both a prompt and '--prompt-len' were given")
+    if g["prompt"] is None and g["prompt_len"] is None:
         _fail("Error: no prompt. Give one as a bare argument or with -p.")
-    g["prompt_ids"] = parse_ids(g["prompt"])
+    g["prompt_ids"] = parse_ids(g["prompt"]) if g["prompt"] is not None else None     # None: drawn once the vocabulary is known
     return g
 
 
@@ -165,12 +178,16 @@ def cmd_run(args) -> int:
     from .engine import Engine, EngineError
     from .weights import SafetensorsError, WeightError
     ids = g["prompt_ids"]
-    ctx = g["max_ctx"] or -(-(len(ids) + g["max_tokens"]) // 64) * 64
+    n_prompt = len(ids) if ids is not None else g["prompt_len"]
+    ctx = g["max_ctx"] or -(-(n_prompt + g["max_tokens"]) // 64) * 64
     try:
         t0 = time.perf_counter()
         from .api import SERVING_PAGE_TOKENS
-        engine = Engine(g["model"], dtype=g["dtype"], max_tokens=ctx, page_tokens=SERVING_PAGE_TOKENS, max_requests=1,
-                        max_context=ctx, max_batch_tokens=max(ctx, 1))
+        engine = Engine(g["model"], dtype=g["dtype"], max_tokens=ctx, page_tokens=g["page_tokens"] or SERVING_PAGE_TOKENS,
+                        max_requests=1, max_context=ctx, max_batch_tokens=max(ctx, 1))
+        if ids is None:
+            import numpy as np
+            ids = np.random.default_rng(g["seed"]).integers(0, engine.vocab, n_prompt).tolist()
         if any(t >= engine.vocab for t in ids):
             print(f"Error: a token id is outside the vocabulary of {engine.vocab}", file=sys.stderr)
             return 1
@@ -211,6 +228,66 @@ def cmd_run(args) -> int:
         return 1
 
 
+def parse_random_args(args):
+    g = dict(config=None, out=None, seed=0, dtype="bfloat16", std=None)
+    i = 0
+    while i < len(args):
+        flag = args[i]
+        if flag == "--seed":
+            g["seed"] = _uint(args, i, flag, 0)
+            i += 2
+        elif flag == "--dtype":
+            v = _need_value(args, i, flag)
+            if v not in ("bfloat16", "float32"):
+                _fail(f"Error: '--dtype' got '{v}', expected bfloat16 or float32")
+            g["dtype"] = v
+            i += 2
+        elif flag == "--std":
+            g["std"] = _float_in(args, i, flag, 0.0, 10.0, "a number from 0 to 10")
+            i += 2
+        elif flag.startswith("-"):
+            _fail(f"Error: unknown argument '{flag}'")
+        elif g["config"] is None:
+            g["config"] = flag
+            i += 1
+        elif g["out"] is None:
+            g["out"] = flag
+            i += 1
+        else:
+            _fail(f"Error: unexpected argument '{flag}'")
+    if g["config"] is None or g["out"] is None:
+        _fail("Error: 'hk random' needs a config.json (or a folder that holds one) and a folder to write")
+    return g
+
+
+def cmd_random(args) -> int:
+    """Writes a model folder with seeded random weights of the architecture that a config.json names (no GPU)."""
+    import os
+    try:
+        g = parse_random_args(args)
+    except BadUsage as e:
+        print(f"{e}\n{USAGE}", file=sys.stderr, end="")
+        return 2
+    import json
+    import torch
+    from .config import ConfigError, config_from_dict
+    from .weights import write_random_model
+    path = os.path.join(g["config"], "config.json") if os.path.isdir(g["config"]) else g["config"]
+    try:
+        with open(path, encoding="utf-8") as f:
+            config = config_from_dict(json.load(f))
+        if os.path.exists(os.path.join(g["out"], "model.safetensors")):
+            print(f"Error: '{g['out']}' already holds a model.safetensors", file=sys.stderr)
+            return 1
+        write_random_model(g["out"], config, g["seed"], std=g["std"],
+                           dtype=torch.float32 if g["dtype"] == "float32" else torch.bfloat16)
+    except (ConfigError, FileNotFoundError, json.JSONDecodeError) as e:
+        print(f"Error: {e}", file=sys.stderr)
+        return 1
+    print(f"wrote {g['out']} ({config.architecture}, seed {g['seed']}, {g['dtype']})", file=sys.stderr)
+    return 0
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if not argv or argv[0] in ("-h", "--help", "help"):
@@ -218,7 +295,9 @@ def main(argv=None) -> int:
         return 0 if argv else 2
     if argv[0] == "run":
         return cmd_run(argv[1:])
-    print(f"Error: unknown command '{argv[0]}' (this engine has 'run')\n{USAGE}", file=sys.stderr, end="")
+    if argv[0] == "random":
+        return cmd_random(argv[1:])
+    print(f"Error: unknown command '{argv[0]}' (this engine has 'run' and 'random')\n{USAGE}", file=sys.stderr, end="")
     return 2
 
 

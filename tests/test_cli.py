@@ -51,3 +51,39 @@ def test_main_reports_usage_errors_with_exit_code_2(capsys):
     err = capsys.readouterr().err
     assert "unknown argument '--wat'" in err and "Usage: hk run" in err
     assert cli.main(["fly"]) == 2
+
+
+def test_prompt_of_a_given_length_and_page_size():
+    g = parse("m", "--prompt-len", "12", "--page-tokens", "16", "--seed", "3")
+    assert g["prompt_ids"] is None and g["prompt_len"] == 12 and g["page_tokens"] == 16
+    with pytest.raises(cli.BadUsage) as e:
+        parse("m", "1,2", "--prompt-len", "4")
+    assert "both a prompt" in str(e.value)
+    with pytest.raises(cli.BadUsage):
+        parse("m", "--prompt-len", "0")
+
+
+def test_random_command_writes_a_model_folder_that_loads(tmp_path, capsys):
+    import json
+    from hk_b200.config import load_config
+    from hk_b200.weights.safetensors_io import SafetensorsFile
+
+    def load_file(path):
+        f = SafetensorsFile(path)
+        return {n: f.tensor(n).clone() for n in f.names()}
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=48, num_hidden_layers=2, intermediate_size=80,
+               num_attention_heads=3, num_key_value_heads=1, head_dim=16, vocab_size=70, rms_norm_eps=1e-6,
+               rope_theta=10000.0, tie_word_embeddings=True, max_position_embeddings=64)
+    (tmp_path / "c.json").write_text(json.dumps(cfg))
+    out = tmp_path / "model"
+    assert cli.main(["random", str(tmp_path / "c.json"), str(out), "--seed", "5", "--dtype", "float32"]) == 0
+    assert load_config(str(out)).hidden_size == 48
+    a = load_file(str(out / "model.safetensors"))
+    assert "model.layers.1.mlp.down_proj.weight" in a and "lm_head.weight" not in a
+    # the same seed gives the same weights; an existing model is not overwritten
+    assert cli.main(["random", str(out), str(tmp_path / "again"), "--seed", "5", "--dtype", "float32"]) == 0
+    b = load_file(str(tmp_path / "again" / "model.safetensors"))
+    assert all((a[k] == b[k]).all() for k in a)
+    assert cli.main(["random", str(out), str(out)]) == 1
+    assert cli.main(["random", str(out)]) == 2
+    assert cli.main(["random", str(out), str(tmp_path / "x"), "--wat"]) == 2

@@ -1,5 +1,6 @@
 """Generation through the entry points, long decoding, the first tokens of a sequence, and the
 device sampler against the plain restatement of the reference's chain."""
+import json
 import os
 import subprocess
 import sys
@@ -376,3 +377,22 @@ def test_command_line_greedy_and_seeds(model_b):
     assert bad.returncode == 2 and "unknown argument" in bad.stderr
     missing = run_cli(os.path.join(d, "nope"), text)
     assert missing.returncode == 1 and "config.json" in missing.stderr
+
+
+def test_command_line_random_model_and_drawn_prompt(tmp_path):
+    """`hk random` writes a model folder from a config.json; `hk run --prompt-len` draws the prompt with the seed; the
+    greedy continuation is the plain implementation's, with 8-token pages as with the default ones."""
+    cfg_json = os.path.join(str(tmp_path), "c.json")
+    with open(cfg_json, "w") as f:
+        json.dump(helpers.TINY_A, f)
+    out = os.path.join(str(tmp_path), "m")
+    made = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "hk"), "random", cfg_json, out, "--seed", "3", "--dtype", "float32"],
+                          capture_output=True, text=True, timeout=600)
+    assert made.returncode == 0, made.stderr
+    cfg, w = helpers.load_plain(out)
+    prompt = np.random.default_rng(5).integers(0, cfg["vocab_size"], 11).tolist()
+    for extra in ([], ["--page-tokens", "8"]):
+        r = run_cli(out, "--prompt-len", "11", "--seed", "5", "-n", "5", "--temp", "0", "--dtype", "float32", *extra)
+        assert r.returncode == 0, r.stderr
+        assert [int(t) for t in r.stdout.split()] == plain_greedy(cfg, w, prompt, 5)
+        assert "[prompt 11 tok" in r.stderr
