@@ -172,6 +172,14 @@ def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
     return True
 
 
+def _tc_partial(lib, M: int, N: int, splits: int, device):
+    """Scratch for the partial sums of `splits` K slices (None without slices)."""
+    if splits <= 1:
+        return None
+    lib.hk_gemm_tc_partial_floats.restype = ctypes.c_longlong
+    return torch.empty(int(lib.hk_gemm_tc_partial_floats(M, N, splits)), dtype=torch.float32, device=device)
+
+
 def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     """out (fp32) = a w^T (+ out).  Returns False when no tensor-core kernel takes the shape."""
     from . import ops
@@ -197,7 +205,7 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
         return True
     lib = build.load("gemm_tc")
     bn, splits = tc_config(M, N, K, _sms(a.device))
-    partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else None
+    partial = _tc_partial(lib, M, N, splits, a.device)
     code = lib.hk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(N), 1 if accumulate else 0, bn,
                           splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:
@@ -224,7 +232,7 @@ def run_swiglu(a, w_paired, out, choice: Optional[str] = None) -> bool:
         return False             # few rows, small weights: the small-M product and the swiglu kernel
     lib = build.load("gemm_tc")
     _, splits = tc_config(M, N, K, _sms(a.device), bn=256)
-    partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device) if splits > 1 else None
+    partial = _tc_partial(lib, M, N, splits, a.device)
     code = lib.hk_gemm_tc(_ptr(a), _ptr(w_paired), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2, 256,
                           splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:

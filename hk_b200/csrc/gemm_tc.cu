@@ -24,6 +24,10 @@
 namespace {
 
 constexpr int BM = 128;
+
+// Floats from one K slice's partial sums to the next: M * N and a pad, so that the same element of all slices
+// does not lie a power of two apart (the kernel that adds the slices reads them together).
+__host__ __device__ inline size_t slice_floats(int M, int N) { return (size_t)M * N + 2080; }
 constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
@@ -134,7 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   // With splits > 1 a work item is (output tile, slice of K); slice s of every tile comes before slice s + 1
   // of any, so the CTAs running together read different weights.  Each item stores its fp32 partial to
-  // partial[s][M][N]; a second kernel adds the slices in order.
+  // partial[s][M][N] (slices `slice_floats` apart); a second kernel adds the slices in order.
   const int mn_tiles = m_tiles * n_tiles;
   const int total_tiles = mn_tiles * splits;
   const int k_blocks_all = (K + BK - 1) / BK;
@@ -230,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
       if (splits > 1) {
         // a slice's partial sum, fp32 [M, N]
-        float* o = partial + ((size_t)ks * M + row) * N + n0;
+        float* o = partial + (size_t)ks * slice_floats(M, N) + (size_t)row * N + n0;
         const int n_out = N - n0;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -378,7 +382,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
   const long long total = MODE == 2 ? (long long)M * (N / 2) : (long long)M * N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const size_t slice = (size_t)M * N;
+  const size_t slice = slice_floats(M, N);
   if (MODE == 2) {
     const int F = N / 2;
     const int m = (int)(i / F), j = (int)(i % F);
@@ -398,6 +402,30 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
   }
 }
 
+// The same sums four columns a thread (16-byte loads and stores; N and ldo multiples of 4), slices in the same order.
+template <int MODE>
+__global__ void splitk_reduce_vec_kernel(const float* __restrict__ partial, float* __restrict__ out, int M, int N, long long ldo,
+                                         int splits) {
+  const long long quads = (long long)M * (N / 4);
+  const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= quads) return;
+  const int m = (int)(q / (N / 4)), n = (int)(q % (N / 4)) * 4;
+  const size_t slice = slice_floats(M, N);
+  const float* p = partial + (size_t)m * N + n;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int s = 0; s < splits; ++s) {
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(p + s * slice));
+    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+  }
+  float4* o = reinterpret_cast<float4*>(out + (size_t)m * ldo + n);
+  if (MODE == 1) {
+    const float4 r = *o;
+    sum.x = r.x + sum.x; sum.y = r.y + sum.y; sum.z = r.z + sum.z; sum.w = r.w + sum.w;
+  }
+  *o = sum;
+}
+
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int splits, float* partial,
            int* status, cudaStream_t s) {
@@ -413,6 +441,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
   gemm_tc_kernel<BN, STAGES, EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, splits, partial, status);
   int code = hk_launch_status();
   if (code != 0 || splits <= 1) return code;
+  if (EPI != EPI_SWIGLU && (N & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0) {
+    const long long quads = (long long)M * (N / 4);
+    splitk_reduce_vec_kernel<EPI == EPI_ADD ? 1 : 0><<<(unsigned)((quads + 127) / 128), 128, 0, s>>>(
+        partial, reinterpret_cast<float*>(out), M, N, ldo, splits);
+    return hk_launch_status();
+  }
   const long long total = EPI == EPI_SWIGLU ? (long long)M * (N / 2) : (long long)M * N;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   splitk_reduce_kernel<EPI><<<blocks, 256, 0, s>>>(partial, out, M, N, ldo, splits);
@@ -426,7 +460,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
 // that a timed-out wait sets to 1 (the caller reads it when it next synchronises).
 // Requirements (else HK_ERR_UNSUPPORTED): K % 8 == 0, a and w 16-byte aligned, for epilogue 2 N % 256 == 0.
 // splits > 1 cuts K into that many slices computed by different CTAs (for few output tiles: decode batches);
-// `partial` must then hold splits * M * N floats of scratch.
+// `partial` must then hold hk_gemm_tc_partial_floats(M, N, splits) floats of scratch.
 HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
                       int splits, float* partial, int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -447,3 +481,6 @@ HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int
   }
   return HK_ERR_UNSUPPORTED;
 }
+
+// Floats of scratch that `hk_gemm_tc` needs for `splits` K slices.
+HK_API long long hk_gemm_tc_partial_floats(int M, int N, int splits) { return (long long)(slice_floats(M, N) * (size_t)splits); }
