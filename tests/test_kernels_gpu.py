@@ -120,7 +120,8 @@ def make_paged(rng, n_slots, lens, G, hd, pt, dtype, extra_pages=3):
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("H,G,hd,pt,rot,norm", [
     (4, 2, 16, 4, 16, True), (5, 1, 48, 16, 24, True), (6, 3, 80, 8, 80, False), (8, 8, 128, 16, 128, True),
-    (3, 1, 256, 32, 64, True), (2, 2, 32, 1, 0, False)])
+    (3, 1, 256, 32, 64, True), (2, 2, 32, 1, 0, False), (3, 1, 40, 8, 24, True), (2, 1, 24, 4, 24, True),
+    (4, 2, 160, 16, 160, True)])
 def test_qk_norm_rope_kv_write(dtype, H, G, hd, pt, rot, norm):
     rng = np.random.default_rng(H * hd + pt)
     lens = [9, 30, 17]
@@ -200,7 +201,7 @@ def test_rotation_reference_fact():
 
 
 ATT_SHAPES = [(4, 2, 16, 4), (5, 1, 48, 16), (6, 2, 80, 8), (8, 2, 128, 16), (3, 3, 256, 16), (7, 7, 32, 32), (8, 1, 64, 16),
-              (2, 1, 112, 16)]
+              (2, 1, 112, 16), (3, 1, 40, 8), (4, 2, 160, 16), (2, 2, 24, 4)]
 
 
 def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=None, sm_count=148, fixed_splits=0):

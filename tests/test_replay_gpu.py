@@ -34,6 +34,7 @@ CASES = {
     "D": dict(lengths=[150, 37, 260, 90], page_tokens=16),
     "E": dict(lengths=[200, 75, 140], page_tokens=32),
     "F": dict(lengths=[3, 50, 121], page_tokens=16),
+    "G": dict(lengths=[45, 8, 97], page_tokens=8),
 }
 
 _cache = {}
@@ -83,7 +84,7 @@ def families(seqs):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E", "F"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "E", "F", "G"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed", "mixed_tight"])
 def test_replay_matches_plain(tmp_path_factory, which, dtype, family):
     from hk_b200.engine import Engine
