@@ -45,6 +45,11 @@ def tc_prefill_supported(hd: int, group: int) -> bool:
     return hd in (64, 128) and group <= 128
 
 
+def split_chunk(span: int, want: int) -> int:
+    """Keys per split when `span` keys (counted from a tile boundary) go to `want` splits: whole tiles."""
+    return -(-(-(-span // want)) // TILE_N) * TILE_N
+
+
 def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
                sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0,
                max_context: int = 0, prefill_rows: int = 64) -> Optional[FlashPlan]:
@@ -89,13 +94,14 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
             want = 1
         else:
             want = max(1, min(2 * sm_count // base_ctas, kv_len // 64, 32))
-        chunk = -(-(-(-kv_len // want)) // TILE_N) * TILE_N
-        n_split = fixed_splits if fixed_splits > 0 else max(1, -(-kv_len // chunk))
+        # splits start on tile boundaries of absolute key positions, so a tile is never shared; the chunk is
+        # sized from that aligned start (at or below kv_lo), so that the last split always reaches kv_hi
+        start = (kv_lo // TILE_N) * TILE_N
+        chunk = split_chunk(kv_hi - start, want)
+        n_split = fixed_splits if fixed_splits > 0 else max(1, -(-(kv_hi - start) // chunk))
         if n_split == 1:
             recs.append((q_row0, n, slot, pos0, kv_lo, kv_hi, -1, 0))
             continue
-        # splits start on tile boundaries of absolute key positions, so a tile is never shared
-        start = (kv_lo // TILE_N) * TILE_N
         for s in range(n_split):
             a = max(kv_lo, start + s * chunk)
             b = min(kv_hi, start + (s + 1) * chunk)
@@ -135,8 +141,8 @@ def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max
     if splits == 1:
         items[:, 0, 4], items[:, 0, 5], items[:, 0, 6] = kv_lo, kv_hi, -1
         return FlashPlan(1, B, upload(items.reshape(B, 8)), 0, max_keys)
-    chunk = -(-(-(-kv_len // splits)) // TILE_N) * TILE_N
     start = (kv_lo // TILE_N) * TILE_N
+    chunk = -(-(-(-(kv_hi - start) // splits)) // TILE_N) * TILE_N     # split_chunk, in array form
     s = np.arange(splits, dtype=np.int64)[None, :]
     a = np.maximum(kv_lo[:, None], start[:, None] + s * chunk[:, None])
     b = np.maximum(a, np.minimum(kv_hi[:, None], start[:, None] + (s + 1) * chunk[:, None]))

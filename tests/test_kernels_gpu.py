@@ -521,6 +521,24 @@ def test_attention_flash_finds_a_far_key(j, fixed_splits):
     assert torch.allclose(got[0, 2], dv[0][j, 1], atol=0.05) and not torch.allclose(got[0, 0], dv[0][j, 1], atol=0.05)
 
 
+@pytest.mark.parametrize("kernel", ["flash", "flash_cp"])
+@pytest.mark.parametrize("window,pos,fixed_splits,sm_count", [(128, 190, 2, 148), (100, 133, 2, 148), (1000, 1500, 16, 148),
+                                                             (128, 133, 0, 4000), (300, 1337, 4, 148), (64, 200, 3, 148)])
+def test_attention_decode_split_keys_reach_the_newest_key_of_a_window(kernel, window, pos, fixed_splits, sm_count):
+    # A window whose first key is no multiple of 64: the splits start at the tile boundary below it, and the last
+    # split must still reach the token's own key.  That key (and then the window's first) is made to dominate.
+    H, G, hd, pt = 4, 2, 64, 16
+    for j in (pos, pos - window + 1):
+        out, want, (_, _, dv, _, _) = attention_case(kernel, torch.bfloat16, H, G, hd, pt, window, [pos + 1], [(pos, 1)],
+                                                     spike=(0, 0, j, 1), sm_count=sm_count, fixed_splits=fixed_splits)
+        close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+        assert torch.allclose(out.double().cpu().reshape(H, hd)[2], dv[0][j, 1], atol=0.05)
+    out, want, (_, _, dv, _, _) = attention_case(kernel, torch.bfloat16, H, G, hd, pt, window, [pos + 1], [(pos, 1)],
+                                                 spike=(0, 0, pos - window, 1), sm_count=sm_count, fixed_splits=fixed_splits)
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)       # the key just outside the window is not seen
+    assert not torch.allclose(out.double().cpu().reshape(H, hd)[2], dv[0][pos - window, 1], atol=0.2)
+
+
 def test_attention_flash_window_edge_in_a_portion():
     # rows at positions 90..99 with window 20: row 99 reads 80..99.  A dominant key at 80 is seen by row 99
     # (the last row of the portion) and one at 79 is not, although rows 90..98 of the same tile do see 79.
