@@ -3,15 +3,19 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 (a "step" is one decode
-step of the whole batch: forward over the paged cache, output head, greedy pick), timed on the
-device with CUDA events after W warm-up steps; every request holds a 2,048-token context when
-the timed steps begin.  `e2e` is the same through the Python entry point (`generate_with_engine`:
-scheduler, host token ids in through pinned memory, sampled ids back to the host every step).
-`prefill` is one 2,048-token prompt in one step; `points` holds decode at batch 1 and 64;
-`roofline` relates the decode step's necessary bytes (every weight once, the cache of the live
-requests) to the measured copy bandwidth.  Each timed step reads about 15 GB of weights, far
-more than the 126 MB L2, so no flush is needed between steps (`l2` in `config` says so).
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 over a cache of 16-token pages
+(a "step" is one decode step of the whole batch: forward over the paged cache, output head, greedy
+pick), timed on the device with CUDA events after W warm-up steps; every request holds a 2,048-token
+context when the timed steps begin.  A timed region is exactly K steps; it is repeated (`regions` in
+`config`) and the median region is reported, with the range in `ms_per_step_range`.  `points` holds the
+same at batch 1 and 64, and at all three batch sizes over 64-token pages (`*_page64`).  `roofline`
+relates the batch-8 step's necessary bytes (every weight once, the cache of the live requests) to the
+measured copy bandwidth; `roofline_points` does so for every batch size.  `e2e` is batch 8 through the
+Python entry point (`generate_with_engine`: scheduler, host token ids in through pinned memory,
+sampled ids back to the host every step); `e2e_points` the same at batch 1 and 64.  `prefill` is one
+2,048-token prompt in one step (median of `--prefill-reps` runs), with its fraction of the measured
+bf16 peak as a burst (`frac`) and sustained (`frac_sustained`).  Each timed step reads about 15 GB of
+weights, far more than the 126 MB L2, so no flush is needed between steps (`l2` in `config` says so).
 """
 from __future__ import annotations
 
@@ -32,7 +36,9 @@ SHAPE = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_la
              rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=8192, initializer_range=0.02)
 CONTEXT = 8192
 PROMPT = 2048
-PAGE = 64
+PAGE = 16             # the cache geometry of the benchmark configuration
+PAGE_EXTRA = 64       # measured as extra points
+REGIONS = 5           # timed regions of K steps each; the median is reported
 SEED = 2
 
 
@@ -136,109 +142,150 @@ def run(args):
     pk = peaks()
     batches = sorted({1, 8, 64} if not args.quick else {1, 8})
     max_b = max(batches)
-    per_req = -(-(PROMPT + args.warmup + args.steps + 8) // 64) * 64
-    t_load = time.time()
-    engine = Engine(config=cfg, random_seed=SEED, dtype="bfloat16", max_tokens=max_b * per_req, page_tokens=PAGE,
-                    max_requests=max_b, max_context=CONTEXT, max_batch_tokens=max(PROMPT, max_b))
-    torch.cuda.synchronize()
-    print(f"[bench] model ready in {time.time() - t_load:.1f} s ({layers} of {layers_full} layers, "
-          f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device)", file=sys.stderr, flush=True)
+    regions = 1 if args.quick else REGIONS
+    per_req = -(-(PROMPT + args.warmup + regions * args.steps + 8) // 64) * 64
     rng = np.random.default_rng(SEED)
     vocab = shape["vocab_size"]
+
+    def make_engine(page):
+        t_load = time.time()
+        eng = Engine(config=cfg, random_seed=SEED, dtype="bfloat16", max_tokens=max_b * per_req, page_tokens=page,
+                     max_requests=max_b, max_context=CONTEXT, max_batch_tokens=max(PROMPT, max_b))
+        torch.cuda.synchronize()
+        print(f"[bench] model ready in {time.time() - t_load:.1f} s ({layers} of {layers_full} layers, {page}-token pages, "
+              f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device)", file=sys.stderr, flush=True)
+        return eng
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
     # ---- prefill of 2,048 tokens (one step), timed on the device ----
-    prompt = rng.integers(0, vocab, PROMPT).tolist()
-    times = []
-    for i in range(args.prefill_reps + 1):
-        engine.open_request("p")
-        a, b = ev(), ev()
-        torch.cuda.synchronize()
-        a.record()
-        engine.step([StepEntry("p", prompt, [PROMPT - 1])])
-        b.record()
-        torch.cuda.synchronize()
-        engine.close_request("p")
-        if i > 0:
-            times.append(a.elapsed_time(b))
-    pre_ms = float(np.median(times))
-    pre = {"value": PROMPT / pre_ms * 1e3, "tokens": PROMPT, "ms": pre_ms,
-           "frac": prefill_flops(shape, layers, PROMPT) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+    def prefill_point(engine):
+        prompt = rng.integers(0, vocab, PROMPT).tolist()
+        times = []
+        for i in range(args.prefill_reps + 2):
+            engine.open_request("p")
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            engine.step([StepEntry("p", prompt, [PROMPT - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            engine.close_request("p")
+            if i > 1:
+                times.append(a.elapsed_time(b))
+        ms = float(np.median(times))
+        flops = prefill_flops(shape, layers, PROMPT)
+        return {"value": PROMPT / ms * 1e3, "tokens": PROMPT, "ms": ms, "frac": flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
+                "frac_sustained": flops / (ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12),
+                "ms_range": [float(min(times)), float(max(times))], "reps": len(times)}
 
-    # ---- decode at batch B: every request holds PROMPT tokens, then W + K single-token steps ----
-    def decode_point(batch, steps, warmup, clocks=None):
+    # ---- decode at batch B: every request holds PROMPT tokens, then W warm-up steps and `regions` regions of K steps ----
+    def decode_point(engine, batch, clocks=None):
+        steps, warmup = args.steps, args.warmup
         ids = [f"d{i}" for i in range(batch)]
-        if clocks is not None:
-            clocks.start()
         for r in ids:
             engine.open_request(r)
         # fill the contexts: real prefill steps, several requests per step
         group = max(1, engine.max_batch_tokens // PROMPT)
         for i in range(0, batch, group):
             engine.step([StepEntry(r, rng.integers(0, vocab, PROMPT).tolist(), []) for r in ids[i:i + group]])
-        toks = rng.integers(0, vocab, (warmup + steps, batch))
+        toks = rng.integers(0, vocab, (warmup + regions * steps, batch))
         out = torch.empty(batch, dtype=torch.int32, device=engine.device)
-        launches0 = None
-        window = [0.0, 0.0]
-        a, b = ev(), ev()
-        for s in range(warmup + steps):
-            if s == warmup:
-                torch.cuda.synchronize()
-                window[0] = time.time()
-                launches0 = ops.launch_count()
-                a.record()
+
+        def one(s):
             logits = engine.step([StepEntry(r, [int(toks[s, i])], [0]) for i, r in enumerate(ids)])
             ops.argmax(logits, out)
-        b.record()
-        torch.cuda.synchronize()
-        window[1] = time.time()
-        ms = a.elapsed_time(b) / steps
-        launches = ops.launch_count() - launches0
+
+        for s in range(warmup):
+            one(s)
+        if clocks is not None:
+            clocks.start()
+            time.sleep(0.3)             # nvidia-smi takes a moment to print its first line
+        ms, launches, window = [], 0, [0.0, 0.0]
+        for reg in range(regions):
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            if reg == 0:
+                window[0] = time.time()
+            l0 = ops.launch_count()
+            a.record()
+            for s in range(warmup + reg * steps, warmup + (reg + 1) * steps):
+                one(s)
+            b.record()
+            torch.cuda.synchronize()
+            window[1] = time.time()
+            ms.append(a.elapsed_time(b) / steps)
+            launches = ops.launch_count() - l0
+        engine.check_kernel_status()
         for r in ids:
             engine.close_request(r)
-        return ms, launches, tuple(window)
+        ctx_mid = PROMPT + warmup + regions * steps // 2
+        nbytes = decode_bytes(shape, layers, batch, ctx_mid)
+        med = float(np.median(ms))
+        achieved = nbytes / (med * 1e-3) / 1e9
+        return {"ms": med, "ms_range": [float(min(ms)), float(max(ms))], "launches": launches, "window": tuple(window),
+                "tok_s": batch / med * 1e3,
+                "roofline": {"bytes": nbytes, "ms": med, "achieved": achieved, "frac": achieved / pk["hbm_gbs"]}}
 
+    # ---- end to end through the Python entry point ----
+    def e2e_point(engine, batch):
+        prompts = [rng.integers(0, vocab, PROMPT).tolist() for _ in range(batch)]
+        st = GenerationStats()
+        generate_with_engine(engine, prompts, max_new_tokens=args.warmup + args.steps + 1, temperature=0, top_k=0,
+                             eos_token_ids=(), prefill_chunk=PROMPT, stats=st)
+        return {"value": st.decode_tokens / max(st.decode_seconds, 1e-9), "unit": "tokens/s",
+                "h2d_bytes_per_step": st.h2d_bytes_per_step, "d2h_bytes_per_step": st.d2h_bytes_per_step}
+
+    engine = make_engine(PAGE)
+    pre = prefill_point(engine)
     clocks = ClockSampler()
-    main_ms, launches, timed = decode_point(8, args.steps, args.warmup, clocks)
-    clock_info = clocks.stop(timed)
-    points = {}
+    dec = {8: decode_point(engine, 8, clocks)}
+    clock_info = clocks.stop(dec[8]["window"])
     for bsz in batches:
-        if bsz == 8:
-            continue
-        ms, _, _ = decode_point(bsz, max(4, args.steps // 2), max(3, args.warmup))
-        points[f"decode_b{bsz}"] = bsz / ms * 1e3
+        if bsz != 8:
+            dec[bsz] = decode_point(engine, bsz)
+    e2e = {bsz: e2e_point(engine, bsz) for bsz in batches}
+    points = {f"decode_b{b}": dec[b]["tok_s"] for b in batches if b != 8}
+    roof_points = {f"decode_b{b}": dec[b]["roofline"] for b in batches}
+    e2e_points = {f"decode_b{b}": e2e[b] for b in batches if b != 8}
+    for b in batches:
+        e2e[b]["of_device_timed"] = e2e[b]["value"] / dec[b]["tok_s"]
+    if not args.quick:
+        # the same decode points over 64-token pages
+        del engine
+        import gc
+        gc.collect()                    # the engine and its captured graphs refer to each other
+        torch.cuda.empty_cache()
+        engine = make_engine(PAGE_EXTRA)
+        for bsz in batches:
+            d = decode_point(engine, bsz)
+            points[f"decode_b{bsz}_page{PAGE_EXTRA}"] = d["tok_s"]
+            roof_points[f"decode_b{bsz}_page{PAGE_EXTRA}"] = d["roofline"]
 
-    # ---- end to end through the Python entry point (batch 8) ----
-    prompts = [rng.integers(0, vocab, PROMPT).tolist() for _ in range(8)]
-    st = GenerationStats()
-    generate_with_engine(engine, prompts, max_new_tokens=args.warmup + args.steps + 1, temperature=0, top_k=0,
-                         eos_token_ids=(), prefill_chunk=PROMPT, stats=st)
-    e2e_steps = max(1, st.decode_steps)
-    e2e = {"value": st.decode_tokens / max(st.decode_seconds, 1e-9), "unit": "tokens/s", "h2d_bytes_per_step": st.h2d_bytes_per_step,
-           "d2h_bytes_per_step": st.d2h_bytes_per_step}
-
-    ctx_mid = PROMPT + args.warmup + args.steps // 2
-    nbytes = decode_bytes(shape, layers, 8, ctx_mid)
-    achieved = nbytes / (main_ms * 1e-3) / 1e9
+    main = dec[8]
     line = {
         "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 2,048-token contexts)",
-        "value": 8 / main_ms * 1e3, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": main_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "value": main["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main["ms"], "ms_per_step_range": main["ms_range"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded uniform token ids, random-init weights N(0, 0.02) seed 2",
         "impl": "ours",
         "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": layers_full, "hidden": shape["hidden_size"],
                    "heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
                    "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"], "vocab": vocab,
                    "global_batch": 8, "seq_len": PROMPT, "context": CONTEXT, "page_tokens": PAGE,
+                   "page_tokens_extra_points": PAGE_EXTRA, "regions": regions,
                    "parallelism": "1 gpu", "l2": "each step reads >15 GB of weights, larger than L2; no flush",
                    "peaks": pk["source"]},
         "prefill": pre,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+        "roofline": {"bound": "hbm", "achieved": main["roofline"]["achieved"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": main["roofline"]["frac"]},
+        "roofline_points": roof_points,
         "points": points,
-        "e2e": e2e,
-        "gpu_launches": launches,
+        "e2e": e2e[8],
+        "e2e_points": e2e_points,
+        "gpu_launches": main["launches"],
         "clocks": clock_info,
     }
     print(json.dumps(line))
@@ -251,7 +298,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in `config`)")
-    ap.add_argument("--prefill-reps", type=int, default=3)
+    ap.add_argument("--prefill-reps", type=int, default=7)
     ap.add_argument("--quick", action="store_true", help="skip batch 64")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -100,6 +100,7 @@ def generate_with_engine(engine: Engine, prompts, max_new_tokens: int = 20, temp
         stats.generated_tokens = sum(len(done[i].output) for i in ids)
         stats.steps = sched.stats.steps
         stats.preemptions = sched.stats.preemptions
+    engine.check_kernel_status()
     return [list(done[i].output) for i in ids]
 
 
@@ -179,7 +180,9 @@ class NativeHKEngine:
         if pos < have:
             self._engine.cache.books.truncate(self._engine.slot_of(0), pos)
         logits = self._engine.step([StepEntry(0, tokens, [len(tokens) - 1])])
-        return logits[0].cpu().numpy()
+        out = logits[0].cpu().numpy()
+        self._engine.check_kernel_status()
+        return out
 
     def forward_step(self, token: int, pos: int) -> np.ndarray:
         return self.forward([token], pos)

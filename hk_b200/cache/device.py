@@ -1,8 +1,9 @@
 """The cache on the GPU: page tensors, block tables and state arrays, driven by `CacheBooks`.
 
-Layout of a group's pages, per schedule entry of the group: keys and values each
-[num_pages, n_kv_heads, page_tokens, head_dim] in the compute type, so one (page, kv head)
-slab of page_tokens * head_dim elements is contiguous.  (The reference keeps a fixed region
+Layout of a group's pages, per cache of the group: keys [num_pages, n_kv_heads, page_tokens,
+k_dim] and values [num_pages, n_kv_heads, page_tokens, v_dim] in the compute type (the two widths
+may differ, and a spec with v_dim 0 keeps the key tensor alone), so one (page, kv head) slab of
+page_tokens * width elements is contiguous.  (The reference keeps a fixed region
 per slot, [layer][kv head][position][head_dim]: src/cuda/engine.zig:234,393-401.)  The block
 table of a group is int32 [max_requests, max_pages_per_request] on the device, a copy of the
 host books' table; rows that changed are uploaded before a step runs.  A mixer with state of
@@ -22,7 +23,7 @@ from .pages import CacheBooks
 @dataclass
 class LayerCache:
     """What one schedule entry's mixer is handed."""
-    kind: str                                  # "pages", "state" or "none"
+    kind: str                                  # "pages" or "state"
     k_pages: Optional[torch.Tensor] = None
     v_pages: Optional[torch.Tensor] = None
     block_table: Optional[torch.Tensor] = None
@@ -35,42 +36,56 @@ class LayerCache:
 class PagedCache:
     def __init__(self, cache_specs: Sequence[object], precision: Precision, page_tokens: int, num_pages: int,
                  max_requests: int, max_context: int):
+        """`cache_specs`: per schedule entry, the list of specs of the caches its block keeps (a bare spec counts
+        as a list of one; None or an empty list: the entry keeps none).  `layers[i]` is the list of `LayerCache`
+        that entry's block is handed, in the order of its specs."""
         self.precision = precision
         self.page_tokens = page_tokens
         self.num_pages = num_pages
-        keys: List[tuple] = []
-        entry_group: List[int] = []
+        entries: List[List[object]] = []
         for spec in cache_specs:
-            if isinstance(spec, KVCacheSpec):
-                key = (spec.n_kv_heads, spec.head_dim, spec.window)
-                if key not in keys:
-                    keys.append(key)
-                entry_group.append(keys.index(key))
+            if spec is None:
+                entries.append([])
+            elif isinstance(spec, (list, tuple)):
+                entries.append([s for s in spec if s is not None])
             else:
-                entry_group.append(-1)
-        self.books = CacheBooks([k[2] for k in keys], page_tokens, num_pages, max_requests, max_context)
+                entries.append([spec])
+        keys: List[tuple] = []
+        for specs in entries:
+            for spec in specs:
+                if isinstance(spec, KVCacheSpec):
+                    key = (spec.n_kv_heads, spec.k_dim, spec.v_dim, spec.window)
+                    if key not in keys:
+                        keys.append(key)
+                elif not isinstance(spec, StateSpec):
+                    raise TypeError(f"a cache spec of type {type(spec).__name__}; KVCacheSpec, StateSpec or None are known")
+        self.books = CacheBooks([k[3] for k in keys], page_tokens, num_pages, max_requests, max_context)
         dev = precision.device
         self.tables = [torch.full((max_requests, self.books.max_pages_per_request), -1, dtype=torch.int32, device=dev)
                        for _ in keys]
         self.uploaded_bytes = 0
-        self.layers: List[LayerCache] = []
+        self.layers: List[List[LayerCache]] = []
         self._states: List[torch.Tensor] = []
-        for spec, gi in zip(cache_specs, entry_group):
-            if isinstance(spec, KVCacheSpec):
-                shape = (num_pages, spec.n_kv_heads, page_tokens, spec.head_dim)
-                # zeros, not empty: a page that was never written must not hold NaN patterns
-                self.layers.append(LayerCache(
-                    "pages", torch.zeros(shape, dtype=precision.compute, device=dev),
-                    torch.zeros(shape, dtype=precision.compute, device=dev), self.tables[gi], page_tokens,
-                    spec.window, None, gi))
-            elif isinstance(spec, StateSpec):
-                st = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=dev)
-                self._states.append(st)
-                self.layers.append(LayerCache("state", state=st))
-            elif spec is None:
-                self.layers.append(LayerCache("none"))
-            else:
-                raise TypeError(f"a mixer's cache_spec() gave {type(spec).__name__}; KVCacheSpec, StateSpec or None are known")
+        for specs in entries:
+            caches: List[LayerCache] = []
+            for spec in specs:
+                if isinstance(spec, KVCacheSpec):
+                    gi = keys.index((spec.n_kv_heads, spec.k_dim, spec.v_dim, spec.window))
+                    # zeros, not empty: a page that was never written must not hold NaN patterns
+                    k = torch.zeros((num_pages, spec.n_kv_heads, page_tokens, spec.k_dim), dtype=precision.compute, device=dev)
+                    v = None
+                    if spec.v_dim > 0:
+                        v = torch.zeros((num_pages, spec.n_kv_heads, page_tokens, spec.v_dim), dtype=precision.compute, device=dev)
+                    caches.append(LayerCache("pages", k, v, self.tables[gi], page_tokens, spec.window, None, gi))
+                else:
+                    st = torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=dev)
+                    self._states.append(st)
+                    caches.append(LayerCache("state", state=st))
+            self.layers.append(caches)
+
+    def has_state(self) -> bool:
+        """Whether any mixer keeps a state of fixed size (which running a row twice would advance twice)."""
+        return bool(self._states)
 
     # -- requests ----------------------------------------------------------------------------
     def open(self) -> int:
@@ -96,8 +111,9 @@ class PagedCache:
 
     def bytes(self) -> int:
         n = 0
-        for lc in self.layers:
-            for t in (lc.k_pages, lc.v_pages, lc.state):
-                if t is not None:
-                    n += t.numel() * t.element_size()
+        for caches in self.layers:
+            for lc in caches:
+                for t in (lc.k_pages, lc.v_pages, lc.state):
+                    if t is not None:
+                        n += t.numel() * t.element_size()
         return n

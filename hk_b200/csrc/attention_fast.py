@@ -50,14 +50,30 @@ def split_chunk(span: int, want: int) -> int:
     return -(-(-(-span // want)) // TILE_N) * TILE_N
 
 
-def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
-               sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0,
-               max_context: int = 0, prefill_rows: int = 64) -> Optional[FlashPlan]:
-    """`upload(int32 array) -> device tensor`.  `fixed_splits` > 0 forces that many items per run
-    (a shape that does not change from step to step, for captured decode graphs); `max_context`
-    then bounds the key range any later step can bring, which sizes the kernel's page-id buffer.
-    `prefill_rows`: rows per CTA for batches with prompt portions: 64 (the mma.sync kernel) or 128 (the
-    tcgen05 kernel, head sizes 64 and 128)."""
+@dataclass
+class PlanInfo:
+    """The host-side facts of a plan: what goes into the kernel launches beside the arrays."""
+    nw: int
+    n_items: int
+    n_parts: int
+    max_keys: int
+
+
+def decode_splits(n_rows: int, n_kv_heads: int, sm_count: int) -> int:
+    """Key splits per request for a decode batch whose plan must keep its shape from step to step: as many
+    CTAs as are resident at once (two per SM), rounded down so that no second, thin wave follows; at most 16,
+    as in the reference (src/cuda/engine.zig:96-101): beyond that the merge of the partials costs more than
+    the split saves."""
+    return max(1, min(16, 2 * sm_count // max(1, n_rows * n_kv_heads)))
+
+
+def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
+                sm_count: int, fixed_splits: int = 0, max_context: int = 0, prefill_rows: int = 64):
+    """The plan on the host: (items int32 [n_items, 8], merge int32 [3, n_tokens] or None, PlanInfo), or None
+    when the kernels do not take this grouping.  `fixed_splits` > 0 forces that many items per run (a shape
+    that does not change from step to step, for captured decode graphs); `max_context` then bounds the key
+    range any later step can bring, which sizes the kernel's page-id buffer.  `prefill_rows`: rows per CTA for
+    batches with prompt portions: 64 (the mma.sync kernel) or 128 (the tcgen05 kernel, head sizes 64 and 128)."""
     group = H // G
     nw = 1 if all(l == 1 for l in q_lens) else prefill_rows // 16
     rows = 16 * nw
@@ -67,7 +83,7 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
         nw, rows = 4, 64
     tpb = rows // group
     if fixed_splits > 0 and nw == 1:
-        return _decode_plan(slots, q_starts, start_positions, n_tokens, window, fixed_splits, max_context, upload)
+        return _decode_plan(slots, q_starts, start_positions, n_tokens, window, fixed_splits, max_context)
     runs = []
     for slot, qs, ql, p0 in zip(slots, q_starts, q_lens, start_positions):
         for b0 in range(0, ql, tpb):
@@ -80,11 +96,8 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
         # longest key ranges first: the heavy items of a causal prompt (its last rows) must not form the tail
         runs.sort(key=lambda r: r[4] - r[5])
     base_ctas = len(runs) * G
-    items = np.zeros((0, 8), dtype=np.int32)
     recs = []
-    first = np.zeros(n_tokens, dtype=np.int32)
-    count = np.zeros(n_tokens, dtype=np.int32)
-    row0 = np.zeros(n_tokens, dtype=np.int32)
+    merge = np.zeros((3, n_tokens), dtype=np.int32)       # per token: first partial, number of partials, row within the item
     n_parts = 0
     for (q_row0, n, slot, pos0, kv_lo, kv_hi) in runs:
         kv_len = kv_hi - kv_lo
@@ -107,20 +120,16 @@ def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: 
             b = min(kv_hi, start + (s + 1) * chunk)
             recs.append((q_row0, n, slot, pos0, a, max(a, b), n_parts + s, 0))
         for tq in range(n):
-            first[q_row0 + tq], count[q_row0 + tq], row0[q_row0 + tq] = n_parts, n_split, tq * group
+            merge[:, q_row0 + tq] = (n_parts, n_split, tq * group)
         n_parts += n_split
     items = np.asarray(recs, dtype=np.int32).reshape(-1, 8)
     max_keys = max((r[5] - r[4] for r in recs), default=0)
     if fixed_splits > 0 and max_context > 0:
         max_keys = max(max_keys, -(-max_context // fixed_splits) + 2 * TILE_N)
-    plan = FlashPlan(nw, len(recs), upload(items), n_parts, max_keys)
-    if n_parts:
-        meta = upload(np.stack([first, count, row0]))
-        plan.first, plan.count, plan.row0 = meta[0], meta[1], meta[2]
-    return plan
+    return items, (merge if n_parts else None), PlanInfo(nw, len(recs), n_parts, max_keys)
 
 
-def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max_context, upload) -> FlashPlan:
+def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max_context):
     """The plan of a batch of single tokens with a fixed number of key splits, in array arithmetic (this runs
     on the host before every replayed decode step).  Same items as the general loop gives."""
     B = len(slots)
@@ -140,7 +149,7 @@ def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max
     items[:, :, 3] = pos[:, None]
     if splits == 1:
         items[:, 0, 4], items[:, 0, 5], items[:, 0, 6] = kv_lo, kv_hi, -1
-        return FlashPlan(1, B, upload(items.reshape(B, 8)), 0, max_keys)
+        return items.reshape(B, 8), None, PlanInfo(1, B, 0, max_keys)
     start = (kv_lo // TILE_N) * TILE_N
     chunk = -(-(-(-(kv_hi - start) // splits)) // TILE_N) * TILE_N     # split_chunk, in array form
     s = np.arange(splits, dtype=np.int64)[None, :]
@@ -148,13 +157,29 @@ def _decode_plan(slots, q_starts, start_positions, n_tokens, window, splits, max
     b = np.maximum(a, np.minimum(kv_hi[:, None], start[:, None] + (s + 1) * chunk[:, None]))
     items[:, :, 4], items[:, :, 5] = a, b
     items[:, :, 6] = np.arange(B, dtype=np.int64)[:, None] * splits + s
-    meta = np.zeros((3, n_tokens), dtype=np.int32)
-    meta[0, qrow] = np.arange(B) * splits
-    meta[1, qrow] = splits
-    plan = FlashPlan(1, B * splits, upload(items.reshape(B * splits, 8)), B * splits, max_keys)
-    m = upload(meta)
-    plan.first, plan.count, plan.row0 = m[0], m[1], m[2]
+    merge = np.zeros((3, n_tokens), dtype=np.int32)
+    merge[0, qrow] = np.arange(B) * splits
+    merge[1, qrow] = splits
+    return items.reshape(B * splits, 8), merge, PlanInfo(1, B * splits, B * splits, max_keys)
+
+
+def plan_on_device(info: PlanInfo, items: torch.Tensor, merge: Optional[torch.Tensor]) -> FlashPlan:
+    plan = FlashPlan(info.nw, info.n_items, items, info.n_parts, info.max_keys)
+    if info.n_parts:
+        plan.first, plan.count, plan.row0 = merge[0], merge[1], merge[2]
     return plan
+
+
+def build_plan(slots, q_starts, q_lens, start_positions, n_tokens: int, window: int, H: int, G: int,
+               sm_count: int, upload: Callable[[np.ndarray], torch.Tensor], fixed_splits: int = 0,
+               max_context: int = 0, prefill_rows: int = 64) -> Optional[FlashPlan]:
+    """`plan_arrays` followed by `upload(int32 array) -> device tensor` for each array."""
+    got = plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens, window, H, G, sm_count, fixed_splits,
+                      max_context, prefill_rows)
+    if got is None:
+        return None
+    items, merge, info = got
+    return plan_on_device(info, upload(items), upload(merge) if merge is not None else None)
 
 
 def _ptr(t):

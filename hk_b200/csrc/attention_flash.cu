@@ -845,12 +845,8 @@ template <int HD, int NW>
 int launch_flash(const void* q, const void* kp, const void* vp, const int* bt, int stride, const void* items, int n_items,
                  void* out, float* part_o, float* part_ml, int H, int G, int pt, int window, float scale_log2, cudaStream_t s) {
   const size_t smem = (size_t)4 * TILE_N * (HD + 8) * sizeof(bf16) + 2 * TILE_N * sizeof(int);
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_flash_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(attention_flash_kernel<HD, NW>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items * (unsigned)G);
   attention_flash_kernel<HD, NW><<<grid, NW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                             (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
@@ -866,12 +862,8 @@ int launch_decode(const void* q, const void* kp, const void* vp, const int* bt, 
   const size_t merge = (size_t)DW * 16 * (HD + 2) * sizeof(float);
   const size_t smem = (tiles > merge ? tiles : merge) + (size_t)pages_cap * sizeof(int);
   if (smem > 200 * 1024) return HK_ERR_UNSUPPORTED;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(attention_decode_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items, (unsigned)G);
   attention_decode_kernel<HD><<<grid, DW * 32, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                          (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, window,
@@ -961,12 +953,8 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
                       float scale_log2, int pages_cap, int* status, cudaStream_t s) {
   const size_t smem = 1024 + (size_t)2 * TS * TT * HD * 2 + 2 * TS * sizeof(uint64_t) + 8 + (size_t)pages_cap * sizeof(int);
   if (smem > 110 * 1024) return HK_ERR_UNSUPPORTED;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(attention_decode_tma_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items, (unsigned)G);
   return hk_launch(attention_decode_tma_kernel<HD>, grid, dim3((TW + 1) * 32), smem, s, mk, mv, (const bf16*)q, bt, stride,
                        (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, pages_cap, status);

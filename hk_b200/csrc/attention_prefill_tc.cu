@@ -505,12 +505,8 @@ int launch(const void* q, const void* kp, const void* vp, const int* bt, int str
            int H, int G, int pt, int window, float scale_log2, int pages_cap, int* status, cudaStream_t s) {
   const size_t smem = sizeof(Smem<HD>) + 1024 + (size_t)pages_cap * sizeof(int);
   if (smem > 225 * 1024) return HK_ERR_UNSUPPORTED;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(attention_prefill_tc_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items * (unsigned)G);
   attention_prefill_tc_kernel<HD><<<grid, NUM_THREADS, smem, s>>>((const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt, stride,
                                                                  (const Item*)items, (bf16*)out, H, G, pt, window, scale_log2,

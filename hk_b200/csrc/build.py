@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_generic": "gemm_generic.cu",
     "attention_generic": "attention_generic.cu",
     "sampling": "sampling.cu",
+    "random_init": "random_init.cu",
     "gemm_tc": "gemm_tc.cu",
     "gemm_smallm": "gemm_smallm.cu",
     "gemm_stream": "gemm_stream.cu",
@@ -42,6 +43,17 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "runtime": "runtime.cpp",          # host only: the cache's books (no GPU code, no CUDA headers)
 }
+
+
+def libraries_for(bfloat16: bool) -> List[str]:
+    """The kernel libraries a model needs: the generic ones always (the 32-bit path, and shapes the fast kernels
+    refuse), the tensor-core and streaming ones only when it computes in bfloat16."""
+    needed = ["elementwise", "gemm_generic", "attention_generic"]
+    if bfloat16:
+        needed += ["gemm_smallm", "gemm_stream", "gemm_tc", "attention_flash", "attention_prefill_tc"]
+    return needed
+
+
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden"]
 HEADERS: List[str] = ["common.cuh", "attention_noalloc.h"]
 

@@ -40,6 +40,27 @@ __device__ __forceinline__ float warp_max(float v) {
 
 static inline int hk_launch_status() { return (int)cudaGetLastError(); }
 
+// Dynamic shared memory above 48 KB has to be allowed per kernel on every device that runs it.  A launcher keeps a
+// `static HkSmemCache` per kernel: the largest size allowed so far on each device (devices beyond the table are
+// set on every launch).  Returns 0 or a cudaError_t.
+#define HK_MAX_DEVICES 64
+struct HkSmemCache {
+  size_t allowed[HK_MAX_DEVICES];
+};
+template <typename K>
+static inline int hk_allow_smem(K kernel, size_t smem, HkSmemCache& cache) {
+  if (smem <= 48 * 1024) return 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  const bool known = dev >= 0 && dev < HK_MAX_DEVICES;
+  if (known && smem <= cache.allowed[dev]) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  if (known) cache.allowed[dev] = smem;
+  return 0;
+}
+
 // Programmatic dependent launch.  A kernel launched with `hk_launch_pdl` may start while the kernel before it
 // in the stream is still running; it must call `pdl_wait()` before it reads or writes anything that an
 // earlier kernel of the stream touches (what it may do before: set up shared memory, read weights and the

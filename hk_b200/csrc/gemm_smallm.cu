@@ -208,13 +208,9 @@ int launch_cluster(void (*kernel)(KArgs...), unsigned grid, int cs, size_t smem,
 template <int MT, int RT, int CS>
 int launch(const void* a, const void* w, float* out, int M, int N, int K, long long ldo, int add, cudaStream_t s) {
   const size_t smem = (size_t)(SM_WARPS + CS - 1) * RT * 16 * MT * 8 * sizeof(float);
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_smallm_kernel<MT, RT, false, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_smallm_kernel<MT, RT, true, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static HkSmemCache allowed_store = {}, allowed_add = {};
+  if (int e = hk_allow_smem(gemm_smallm_kernel<MT, RT, false, CS>, smem, allowed_store)) return e;
+  if (int e = hk_allow_smem(gemm_smallm_kernel<MT, RT, true, CS>, smem, allowed_add)) return e;
   const unsigned grid = (unsigned)((N + RT * 16 - 1) / (RT * 16)) * CS;
   if (CS > 1) {
     if (add)

@@ -410,12 +410,8 @@ int launch(const void* a, const void* w, void* out, int M, int N, int K, long lo
   using S = Shape<RW, MT>;
   CUtensorMap ma, mw;
   if (!make_map(&ma, a, M, K, 8 * MT, S::KW) || !make_map(&mw, w, N, K, S::BN / 2, S::KW)) return HK_ERR_UNSUPPORTED;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<RW, MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(gemm_stream_kernel<RW, MT, EPI>, (size_t)S::SMEM, allowed)) return e;
   const int n_tiles = EPI == EPI_SWIGLU ? N / S::BN : (N + S::BN - 1) / S::BN;
   const long long units = (long long)n_tiles * ((K + S::BK - 1) / S::BK);
   long long grid = sm_count();

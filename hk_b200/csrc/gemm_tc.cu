@@ -429,13 +429,9 @@ __global__ void splitk_reduce_vec_kernel(const float* __restrict__ partial, floa
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int splits, float* partial,
            int* status, cudaStream_t s) {
-  static bool configured = false;
+  static HkSmemCache allowed = {};
   const size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  if (int e = hk_allow_smem(gemm_tc_kernel<BN, STAGES, EPI>, smem, allowed)) return e;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_tc_kernel<BN, STAGES, EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, splits, partial, status);

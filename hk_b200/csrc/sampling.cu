@@ -387,13 +387,9 @@ HK_API int hk_sample(const float* logits, int rows, int V, const float* temperat
                      const float* top_p, const float* min_p, const unsigned long long* seeds,
                      const unsigned long long* counters, int* out, void* stream) {
   if (rows <= 0) return 0;
-  static bool configured = false;
+  static HkSmemCache allowed = {};
   size_t smem = sizeof(SampleShared);
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  if (int e = hk_allow_smem(sample_kernel, smem, allowed)) return e;
   sample_kernel<<<rows, SMP_THREADS, smem, (cudaStream_t)stream>>>(logits, V, temperature, top_k, top_p, min_p, seeds,
                                                                  counters, out);
   return hk_launch_status();

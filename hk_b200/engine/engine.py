@@ -5,7 +5,7 @@ of prompts beside single decoded tokens, cut anywhere.  It runs only those token
 batch, over the cache that earlier steps left, and returns the float32 logits at the wanted
 places.  This is the reference's `forwardItems` + `logitsMany`
 (src/engine/model.zig:292-343): a flat list of items mixing sequences, K/V of the whole
-batch written before attention (src/engine/cpu_backend.zig:290-295), logits only for the
+batch written before any score is taken (src/engine/cpu_backend.zig:290-295), logits only for the
 asked rows (cpu_backend.zig:342-357).  Errors (`BatchTooLarge`, `ContextFull`,
 `TokenOutOfRange`, `OutOfPages`; cf. src/engine/model.zig:53-59,296-300) are raised before
 anything changes, and the engine stays usable (tests/test_engine.zig:189-203 holds the
@@ -24,7 +24,7 @@ from ..cache.pages import CacheError, ContextFull, OutOfPages
 from ..config import ModelConfig, load_config, resolve_architecture
 from ..parts.base import Precision
 from ..weights.loader import load_tensors, random_tensors
-from .context import StepContext
+from .context import StepContext, bind_step, pack_step, table_parts
 
 
 class EngineError(RuntimeError):
@@ -165,10 +165,7 @@ class Engine:
         self.max_batch_tokens = int(max_batch_tokens)
         # compile, side by side, the kernel libraries this precision runs on (and only those)
         from ..csrc import build as _build
-        needed = ["elementwise", "gemm_generic", "attention_generic"]
-        if self.precision.compute == torch.bfloat16:
-            needed += ["gemm_smallm", "gemm_stream", "gemm_tc", "attention_flash", "attention_prefill_tc"]
-        _build.build_many(needed)
+        _build.build_many(_build.libraries_for(self.precision.compute == torch.bfloat16))
         self.model = build_model(config, self.max_context)
         specs = self.model.param_specs()
         with torch.no_grad():
@@ -193,9 +190,13 @@ class Engine:
             from ..csrc import gemm_fast
             self._kernel_status = gemm_fast.status_flag(self.device)
             self._kernel_status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self.plan_builder = self._flash_plan if self.precision.compute == torch.bfloat16 else None
+        # the parts that want host-built tables in every step (one per distinct key), found once
+        self._table_parts = table_parts(self.model)
         from .graphs import model_is_graph_safe
         self.decode_graphs = bool(decode_graphs) and model_is_graph_safe(self.model)
+        # a batch may be filled up with repeats of its last row only if running a row twice changes nothing:
+        # true of key/value pages (the same values are written again), false of a state that is advanced
+        self._pad_graphs = not self.cache.has_state()
         self._graphs: Dict[int, object] = {}
 
     # -- requests ----------------------------------------------------------------------------
@@ -225,13 +226,6 @@ class Engine:
 
     def free_pages(self) -> List[int]:
         return self.cache.books.free_pages()
-
-    def _flash_plan(self, ctx: StepContext, window: int, n_heads: int, n_kv_heads: int, head_dim: int):
-        from ..csrc import attention_fast, ops
-        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        tc = attention_fast.tc_prefill_supported(head_dim, n_heads // n_kv_heads) and ops.forced("attention") != "flash_cp"
-        return attention_fast.build_plan(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens, window,
-                                         n_heads, n_kv_heads, sms, self.stager.upload, prefill_rows=128 if tc else 64)
 
     # -- the step function -------------------------------------------------------------------
     def check_step(self, entries: Sequence[StepEntry]) -> None:
@@ -291,6 +285,17 @@ class Engine:
             raise KernelTimeout("a tensor-core kernel gave up waiting on a barrier in an earlier step; "
                                 "the logits and the cache since then are invalid")
 
+    def check_kernel_status(self) -> None:
+        """Waits for everything launched so far and raises `KernelTimeout` if a kernel of any step gave up a
+        bounded wait.  `step` itself looks at the word only when the next step begins and without waiting, so
+        whoever hands results to the host after a last step (generation, the replay program, a benchmark)
+        calls this first."""
+        if self._kernel_status is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self._kernel_status_host[0] = int(self._kernel_status.item())
+        self._check_kernel_status()
+
     def _run_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         books = self.cache.books
         slots = [self.slot_of(e.request) for e in entries]
@@ -324,7 +329,7 @@ class Engine:
             # a graph per batch size would be captured again whenever a request comes or goes; sizes above 8 are
             # rounded up to the next multiple of 8 and the batch is filled with repeats of its last row (the same
             # token at the same place: it writes the same key and value again and its logits are dropped)
-            nb = graph_batch(n)
+            nb = graph_batch(n) if self._pad_graphs else n
             if nb > n:
                 meta = np.concatenate([meta, np.repeat(meta[:, -1:], nb - n, axis=1)], axis=1)
                 if on_device and on_device[-1][0] == n - 1:
@@ -336,10 +341,11 @@ class Engine:
                 g = self._graphs[nb] = DecodeGraph(self, nb)
             self.steps_run += 1
             return g.run(meta, slots, starts, on_device, n)
-        meta_dev = self.stager.upload(meta)
-        fill_device_tokens(meta_dev[0], on_device)
-        ctx = StepContext(self.precision, n, meta_dev[0], meta_dev[1], meta_dev[2], slots, q_starts, q_lens,
-                          starts, plan_builder=self.plan_builder)
+        ctx = StepContext(self.precision, n, None, None, None, slots, q_starts, q_lens, starts,
+                          max_context=self.max_context)
+        packed = pack_step(meta, ctx, self._table_parts)
+        bind_step(ctx, packed, self.stager.upload(packed.host))
+        fill_device_tokens(ctx.token_ids, on_device)
         x = self.model.forward(ctx, self.cache.layers)
         self.steps_run += 1
         if not rows:

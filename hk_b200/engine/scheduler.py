@@ -337,4 +337,7 @@ class Scheduler:
         """Steps until every submitted request has finished."""
         while self.has_work():
             self.step()
+        check = getattr(self.engine, "check_kernel_status", None)
+        if check is not None:
+            check()
         return self.finished

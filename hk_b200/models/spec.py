@@ -49,13 +49,14 @@ class ModelSpec(Part):
         return self.head.vocab
 
     def cache_specs(self):
-        """For each schedule entry: the spec of the cache it keeps, or None (keeps none)."""
+        """For each schedule entry: the specs of the caches its block keeps (a list, as the block gives it), or
+        None for an entry that keeps none and reads another entry's."""
         out = []
         for call in self.schedule:
             if call.cache_of is not None:
                 out.append(None)
             else:
-                out.append(self.layers[call.layer].mixer.cache_spec())
+                out.append(list(self.layers[call.layer].cache_specs()))
         return out
 
     def forward(self, ctx, caches) -> torch.Tensor:

@@ -1,5 +1,5 @@
 from .attention import GQAAttention
-from .base import (KVCacheSpec, MATRIX, ParamSpec, Part, Precision, StateSpec, TABLE, VECTOR, part_class,
+from .base import (KVCacheSpec, MATRIX, ParamSpec, Part, Precision, StateSpec, StepTables, TABLE, VECTOR, part_class,
                    register_part)
 from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
@@ -9,6 +9,6 @@ from .position import RotaryEmbedding
 
 __all__ = [
     "GQAAttention", "KVCacheSpec", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
-    "RMSNorm", "RotaryEmbedding", "StateSpec", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
+    "RMSNorm", "RotaryEmbedding", "StateSpec", "StepTables", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
     "part_class", "register_part",
 ]

@@ -22,7 +22,7 @@ from typing import Dict, Optional
 import torch
 
 from ..csrc import ops
-from .base import KVCacheSpec, MATRIX, VECTOR, ParamSpec, Part, Precision, register_part
+from .base import KVCacheSpec, MATRIX, VECTOR, ParamSpec, Part, Precision, StepTables, register_part
 from .position import RotaryEmbedding
 
 
@@ -45,6 +45,8 @@ class GQAAttention(Part):
         self.window = window
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self._tables_key = None        # set at bind: the flash kernels' work items, when they take these sizes
+        self._sm_count = 0
 
     # -- declaration ---------------------------------------------------------------------
     def children(self):
@@ -75,14 +77,47 @@ class GQAAttention(Part):
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[p + "q_norm.weight"]
             self.k_norm = tensors[p + "k_norm.weight"]
+        from ..csrc import attention_fast
+        if precision.compute == torch.bfloat16 and attention_fast.supported(self.hd, self.H // self.G):
+            self._tables_key = ("paged_attention_items", self.window or 0, self.H, self.G, self.hd)
+            self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
+
+    # -- the step's work items (host-built; see parts.base) --------------------------------
+    def step_tables_key(self):
+        return self._tables_key
+
+    def step_tables(self, ctx):
+        """Cuts the batch into the flash kernels' work items (csrc/attention_fast.py).  In a step whose shape must
+        not change (a captured decode graph) every request's keys go to the same number of splits."""
+        from ..csrc import attention_fast
+        H, G, hd = self.H, self.G, self.hd
+        tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp"
+        fixed = attention_fast.decode_splits(ctx.n_tokens, G, self._sm_count) if ctx.fixed_shape else 0
+        got = attention_fast.plan_arrays(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens,
+                                         self.window or 0, H, G, self._sm_count, fixed_splits=fixed,
+                                         max_context=ctx.max_context if ctx.fixed_shape else 0,
+                                         prefill_rows=128 if tc else 64)
+        if got is None:
+            return None
+        items, merge, info = got
+        arrays = {"items": items}
+        if merge is not None:
+            arrays["merge"] = merge
+        return StepTables(arrays, info)
+
+    def _plan(self, ctx):
+        got = ctx.tables.get(self._tables_key) if self._tables_key is not None else None
+        if got is None or got[1] is None:
+            return None                    # no work items: the generic kernel takes the step
+        from ..csrc import attention_fast
+        arrays, info = got
+        return attention_fast.plan_on_device(info, arrays["items"], arrays.get("merge"))
 
     # -- one step ------------------------------------------------------------------------
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True) -> None:
         n = xb.shape[0]
         H, G, hd = self.H, self.G, self.hd
-        # the attention work items are uploaded before any kernel of this layer is launched (kernels may start
-        # ahead of their predecessor and read such host-written tables early)
-        plan = ctx.attention_plan(self.window or 0, H, G, hd) if xb.dtype == torch.bfloat16 else None
+        plan = self._plan(ctx) if xb.dtype == torch.bfloat16 else None
         qkv = torch.empty((n, (H + 2 * G) * hd), dtype=torch.float32, device=xb.device)
         ops.gemm(xb, self.w_qkv, qkv)
         q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)

@@ -57,6 +57,7 @@ def main(argv=None) -> int:
         logits = engine.step(entries)
         if logits is not None:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+            engine.check_kernel_status()          # no logits leave with a kernel's time-out unreported
             tmp = os.path.join(args.out, f".{step}.f32.tmp")
             arr.tofile(tmp)
             os.replace(tmp, os.path.join(args.out, f"{step}.f32"))

@@ -12,7 +12,6 @@ float32 on the true 32-bit path), vectors in float32, integer tables in int32.
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 from typing import Dict, Optional
@@ -87,33 +86,48 @@ def load_tensors(model_dir: str, specs: Dict[str, ParamSpec], precision: Precisi
     return out
 
 
-def _seed_of(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
 def random_tensors(specs: Dict[str, ParamSpec], seed: int, std: float, norm_std: float,
                    device, dtype_of=None) -> Dict[str, torch.Tensor]:
     """Seeded random values for every declared, non-optional tensor: matrices N(0, std),
     norm-like vectors 1 + N(0, norm_std).  Each tensor has a stream of its own, derived from
-    (seed, name), so the values do not depend on the order or on which other tensors exist.
-    Values are drawn in float32 on `device` and cast to `dtype_of(spec)` (default float32)."""
+    (seed, name), so the values do not depend on the order or on which other tensors exist, and
+    the stream is counter-based with fixed arithmetic (`random_stream`), so they do not depend on
+    the device either: a CUDA device fills the tensors with a kernel, the CPU with numpy, and
+    both hold the same bits.  Values are made in float32 and cast to `dtype_of(spec)`
+    (default float32)."""
+    from . import random_stream
     device = torch.device(device)
     out = {}
     for name, spec in specs.items():
         if spec.optional:
             continue
-        gen = torch.Generator(device=device)
-        gen.manual_seed(_seed_of(seed, name))
         if spec.kind == TABLE:
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
-        if spec.init == "one_plus_normal":
-            t.mul_(norm_std).add_(1.0)
+        dtype = dtype_of(spec) if dtype_of is not None else torch.float32
+        key = random_stream.tensor_key(seed, name)
+        count = 1
+        for n in spec.shape:
+            count *= int(n)
+        one_plus = spec.init == "one_plus_normal"
+        scale, offset = (norm_std, 1.0) if one_plus else (std, 0.0)
+        if device.type == "cuda" and dtype in (torch.float32, torch.bfloat16):
+            import ctypes
+
+            from ..csrc import build
+            lib = build.load("random_init")
+            t = torch.empty(spec.shape, dtype=dtype, device=device)
+            with torch.cuda.device(device):
+                code = lib.hk_random_init(ctypes.c_void_p(t.data_ptr()), 0 if dtype == torch.float32 else 1,
+                                          ctypes.c_longlong(count), ctypes.c_ulonglong(key), ctypes.c_float(scale),
+                                          ctypes.c_float(offset), 1 if one_plus else 0,
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            if code != 0:
+                raise RuntimeError(f"random_init: CUDA error {code}")
+            out[name] = t
         else:
-            t.mul_(std)
-        out[name] = t.to(dtype_of(spec)) if dtype_of is not None else t
+            host = torch.from_numpy(random_stream.fill(key, count, scale, offset)).reshape(spec.shape)
+            out[name] = host.to(dtype).to(device)
     return out
 
 
@@ -126,8 +140,11 @@ def write_random_model(model_dir: str, config, seed: int, std: Optional[float] =
     spec = build_model(config, 8)
     if std is None:
         std = float(getattr(config, "initializer_range", 0.02))
-    tensors = random_tensors(spec.param_specs(), seed, std, norm_std, "cpu",
+    # the same bits on either device; a GPU, where there is one, fills large models in seconds
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    tensors = random_tensors(spec.param_specs(), seed, std, norm_std, device,
                              dtype_of=lambda s: torch.int32 if s.kind == TABLE else dtype)
+    tensors = {k: v.cpu() for k, v in tensors.items()}
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config.to_dict(), f, indent=1)

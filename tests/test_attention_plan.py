@@ -92,12 +92,8 @@ def test_decode_plan_in_array_arithmetic_equals_the_general_loop():
         splits = int(rng.choice([2, 4, 16]))
         B = int(rng.integers(1, 9))
         pos = [int(rng.integers(0, 7000)) for _ in range(B)]
-        ups = []
-        fast = attention_fast._decode_plan(list(range(B)), list(range(B)), pos, B, window, splits, 8192,
-                                           lambda a: (ups.append(np.array(a)), torch.from_numpy(np.ascontiguousarray(a)))[1])
-        # the general loop, made to take the same number of splits by prefill_rows that keep nw at 1 impossible:
-        # restate it here from its definition instead
-        items = ups[0].reshape(B, splits, 8)
+        items, merge, info = attention_fast._decode_plan(list(range(B)), list(range(B)), pos, B, window, splits, 8192)
+        items = items.reshape(B, splits, 8)
         for i, p in enumerate(pos):
             kv_hi = p + 1
             kv_lo = max(0, p - window + 1) if window > 0 else 0
@@ -107,4 +103,4 @@ def test_decode_plan_in_array_arithmetic_equals_the_general_loop():
                 a = max(kv_lo, start + s * chunk)
                 b = max(a, min(kv_hi, start + (s + 1) * chunk))
                 assert (int(items[i, s, 4]), int(items[i, s, 5])) == (a, b)
-        assert fast.n_parts == B * splits
+        assert info.n_parts == B * splits and merge.shape == (3, B)

@@ -6,8 +6,11 @@ latency or its synchronisation, a plugin that is only ever handed device pointer
 `hk_attention_decode_noalloc` keeps the partial results of split key ranges in an array inside
 the library image instead of caller-allocated scratch.  This test calls it through its exported
 C symbol, twice in a row and once more with the first inputs (the shared array then holds another
-call's leftovers), and compares with the ordinary entry point on the same inputs.  It also checks
-that a request beyond the array's stated size is refused and that torch's allocator saw nothing.
+call's leftovers), and compares with the ordinary entry point on the same inputs and with the plain
+per-kernel reference (`ref_ops.paged_attention`), so that a fault shared by both entry points shows too.
+It also checks that a request beyond the array's stated size is refused, and that the driver's count of
+free device memory is the same before and after the calls (torch's allocator cannot see a cudaMalloc made
+inside a C entry point; the driver's figure can).
 
 The file sorts last on purpose: a run that stops at the first failure has then run everything else.
 """
@@ -38,8 +41,15 @@ def make_case(seed, H, G, hd, pt, lens, splits, window):
     plan = attention_fast.build_plan(list(range(n)), list(range(n)), [1] * n, [l - 1 for l in lens], n, window, H, G, 148,
                                      lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV), fixed_splits=splits)
     assert plan.nw == 1 and plan.n_parts == n * splits
+    import ref_ops
+    want = ref_ops.paged_attention(q, k_pages, v_pages, bt, pos, slot, H, G, hd, pt, window, 1.0 / math.sqrt(hd))
     return dict(q=q.to(DEV), k=k_pages.to(DEV), v=v_pages.to(DEV), bt=bt.to(DEV), pos=pos.to(DEV), slot=slot.to(DEV),
-                plan=plan, H=H, G=G, hd=hd, pt=pt, window=window, n=n)
+                plan=plan, H=H, G=G, hd=hd, pt=pt, window=window, n=n, plain=want.reshape(n, H * hd))
+
+
+def close_to(got, want):
+    diff = (got.double().cpu() - want.double().cpu()).abs()
+    assert (diff <= 3e-3 + 2 ** -7 * want.double().cpu().abs()).all(), f"worst {diff.max():.3g}"
 
 
 def ordinary(case):
@@ -65,20 +75,24 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_on_calls_in_a_row():
     from hk_b200.csrc import build
     lib = build.load("attention_flash")
     a = make_case(1, 8, 2, 128, 16, [700, 64, 129, 333], 5, 0)
+    # b: windows of 40 and 100 keys whose first key is no multiple of the 64-key tile (257 - 40, 190 - 100)
     b = make_case(2, 6, 3, 64, 8, [90, 257, 31], 3, 40)
-    want_a, want_b = ordinary(a), ordinary(b)
-    outs = [torch.empty_like(a["q"]), torch.empty_like(b["q"]), torch.empty_like(a["q"])]
+    c = make_case(4, 4, 2, 64, 16, [191, 134], 2, 100)
+    want_a, want_b, want_c = ordinary(a), ordinary(b), ordinary(c)
+    outs = [torch.empty_like(a["q"]), torch.empty_like(b["q"]), torch.empty_like(a["q"]), torch.empty_like(c["q"])]
+    warm = torch.empty_like(a["q"])
+    assert no_alloc(lib, a, warm) == 0          # the first call on a device resolves the array's address
     torch.cuda.synchronize()
-    allocs = torch.cuda.memory_stats()["allocation.all.allocated"]
-    in_use = torch.cuda.memory_allocated()
-    codes = [no_alloc(lib, a, outs[0]), no_alloc(lib, b, outs[1]), no_alloc(lib, a, outs[2])]
+    free_before, _ = torch.cuda.mem_get_info()
+    codes = [no_alloc(lib, a, outs[0]), no_alloc(lib, b, outs[1]), no_alloc(lib, a, outs[2]), no_alloc(lib, c, outs[3])]
     torch.cuda.synchronize()
-    assert codes == [0, 0, 0]
-    assert torch.cuda.memory_stats()["allocation.all.allocated"] == allocs and torch.cuda.memory_allocated() == in_use
-    for got, want in ((outs[0], want_a), (outs[1], want_b), (outs[2], want_a)):
-        diff = (got.double() - want.double()).abs()
-        assert (diff <= 3e-3 + 2 ** -7 * want.double().abs()).all(), f"worst {diff.max():.3g}"
-    assert torch.equal(outs[0], outs[2])
+    free_after, _ = torch.cuda.mem_get_info()
+    assert codes == [0, 0, 0, 0]
+    assert free_after == free_before, "the entry point took device memory from the driver"
+    for got, want, case in ((outs[0], want_a, a), (outs[1], want_b, b), (outs[2], want_a, a), (outs[3], want_c, c)):
+        close_to(got, want)
+        close_to(got, case["plain"])
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[0], warm)
 
 
 def test_no_alloc_entry_point_refuses_what_its_array_cannot_hold():
@@ -94,3 +108,4 @@ def test_no_alloc_entry_point_refuses_what_its_array_cannot_hold():
     assert no_alloc(lib, a, out) == 0
     torch.cuda.synchronize()
     assert torch.equal(out, ordinary(a))
+    close_to(out, a["plain"])
