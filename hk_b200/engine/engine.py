@@ -147,7 +147,7 @@ class Engine:
 
     def __init__(self, model_dir: Optional[str] = None, *, config: Optional[ModelConfig] = None,
                  random_seed: Optional[int] = None, random_std: Optional[float] = None,
-                 random_norm_std: float = 0.05, dtype="bfloat16", max_tokens: int = 8192,
+                 random_norm_std: float = 0.05, random_dtype=None, dtype="bfloat16", max_tokens: int = 8192,
                  page_tokens: int = 16, max_requests: int = 8, max_context: Optional[int] = None,
                  max_batch_tokens: int = 8192, device: int = 0, decode_graphs: bool = True):
         self.device = _resolve_device(device)
@@ -171,8 +171,17 @@ class Engine:
         with torch.no_grad():
             if random_seed is not None:
                 std = random_std if random_std is not None else float(getattr(config, "initializer_range", 0.02))
-                tensors = random_tensors(specs, random_seed, std, random_norm_std, self.device,
-                                         dtype_of=lambda s: self.precision.working_dtype(s.kind))
+                # `random_dtype`: the type a model folder of these weights would store its matrices in (they are
+                # rounded to it first, then held in the working type): a 32-bit engine with random_dtype bfloat16
+                # computes with exactly the matrices of the bfloat16 engine of the same seed
+                stored = parse_dtype(random_dtype) if random_dtype is not None else None
+
+                def dtype_of(s):
+                    work = self.precision.working_dtype(s.kind)
+                    return stored if stored is not None and s.kind == "matrix" and work == torch.float32 else work
+                tensors = random_tensors(specs, random_seed, std, random_norm_std, self.device, dtype_of=dtype_of)
+                if stored is not None:
+                    tensors = {k: v.to(self.precision.working_dtype(specs[k].kind)) for k, v in tensors.items()}
             else:
                 tensors = load_tensors(model_dir, specs, self.precision)
             self.model.bind(tensors, self.precision)

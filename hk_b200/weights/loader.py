@@ -18,7 +18,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..parts.base import ParamSpec, Precision, TABLE
+from ..parts.base import ParamSpec, Precision, TABLE, VECTOR
 from .safetensors_io import SafetensorsError, open_model_files, save_file
 
 _FLOAT_DTYPES = (torch.float32, torch.float16, torch.bfloat16, torch.float64)
@@ -134,7 +134,9 @@ def random_tensors(specs: Dict[str, ParamSpec], seed: int, std: float, norm_std:
 def write_random_model(model_dir: str, config, seed: int, std: Optional[float] = None,
                        norm_std: float = 0.05, dtype: torch.dtype = torch.bfloat16) -> None:
     """Writes a model folder (config.json, model.safetensors) with seeded random weights of
-    `config`'s architecture.  `std` defaults to the configuration's `initializer_range`."""
+    `config`'s architecture.  `std` defaults to the configuration's `initializer_range`.  Matrices are stored
+    as `dtype`; vectors (norm weights) in float32, the type every engine computes them in, so that an engine that
+    loads the folder and an engine given the same seed hold the same values."""
     from ..config import resolve_architecture
     _, build_model = resolve_architecture(config.architecture)
     spec = build_model(config, 8)
@@ -143,7 +145,7 @@ def write_random_model(model_dir: str, config, seed: int, std: Optional[float] =
     # the same bits on either device; a GPU, where there is one, fills large models in seconds
     device = "cuda" if torch.cuda.is_available() else "cpu"
     tensors = random_tensors(spec.param_specs(), seed, std, norm_std, device,
-                             dtype_of=lambda s: torch.int32 if s.kind == TABLE else dtype)
+                             dtype_of=lambda s: {TABLE: torch.int32, VECTOR: torch.float32}.get(s.kind, dtype))
     tensors = {k: v.cpu() for k, v in tensors.items()}
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:

@@ -35,7 +35,13 @@ SHAPES = {
 PAGE = 64
 
 
-def _engine(name: str, layers: int, seed: int, lengths, max_batch_tokens: int):
+def _opt(args, name, default):
+    """An override of a workload's constants (tests run the workloads small, greedy and in either precision)."""
+    v = getattr(args, name, None)
+    return default if v is None else v
+
+
+def _engine(name: str, layers: int, seed: int, lengths, max_batch_tokens: int, dtype: str = "bfloat16"):
     from .config import config_from_dict
     from .engine import Engine
     shape = dict(SHAPES[name])
@@ -44,7 +50,7 @@ def _engine(name: str, layers: int, seed: int, lengths, max_batch_tokens: int):
     cfg = config_from_dict(dict(architectures=["Qwen3ForCausalLM"], rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
                                 max_position_embeddings=8192, initializer_range=0.02, **shape))
     tokens = sum(-(-n // PAGE) * PAGE for n in lengths)
-    eng = Engine(config=cfg, random_seed=seed, dtype="bfloat16", max_tokens=tokens, page_tokens=PAGE, max_requests=len(lengths),
+    eng = Engine(config=cfg, random_seed=seed, dtype=dtype, max_tokens=tokens, page_tokens=PAGE, max_requests=len(lengths),
                  max_context=8192, max_batch_tokens=max_batch_tokens)
     return cfg, eng
 
@@ -62,20 +68,24 @@ def serve14b(args) -> dict:
     from .engine.scheduler import Scheduler
     from .sampling import SamplingParams
     rng = np.random.default_rng(3)
-    n_req, new = 32, 128
-    lens = rng.integers(128, 4097, n_req).tolist()
-    cfg, eng = _engine("serve14b", args.layers, 3, [n + new for n in lens], max_batch_tokens=2048)
+    n_req, new = 32, _opt(args, "new_tokens", 128)
+    lo, hi = _opt(args, "prompt_range", (128, 4096))
+    temperature = _opt(args, "temperature", 0.8)
+    lens = rng.integers(lo, hi + 1, n_req).tolist()
+    cfg, eng = _engine("serve14b", args.layers, 3, [n + new for n in lens], max_batch_tokens=2048, dtype=_opt(args, "dtype", "bfloat16"))
     prompts = [rng.integers(0, cfg.vocab_size, n).tolist() for n in lens]
 
     def once():
-        sched = Scheduler(eng, prefill_chunk=512)
-        ids = [sched.submit(p, new, SamplingParams(temperature=0.8, top_k=0, top_p=1.0, min_p=0.0, seed=100 + i))
+        sched = Scheduler(eng, prefill_chunk=_opt(args, "portion", 512))
+        ids = [sched.submit(p, new, SamplingParams(temperature=temperature, top_k=0, top_p=1.0, min_p=0.0, seed=100 + i))
                for i, p in enumerate(prompts)]
         counters = {"mixed_steps": 0}
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         _drain(sched, counters)
         torch.cuda.synchronize()
+        if _opt(args, "keep_tokens", False):
+            args.kept = (cfg, prompts, [list(sched.finished[i].output) for i in ids])
         return sched, counters, time.perf_counter() - t0, sum(len(sched.finished[i].output) for i in ids)
 
     first = once()[2]            # loads the kernels and captures the decode graphs of every batch size it meets
@@ -85,25 +95,28 @@ def serve14b(args) -> dict:
             "requests": n_req, "prompt_tokens": int(sum(lens)), "generated_tokens": out, "seconds": dt, "first_run_seconds": first,
             "tokens_per_s": (sum(lens) + out) / dt, "generated_per_s": out / dt, "steps": sched.stats.steps,
             "mixed_steps": counters["mixed_steps"], "ahead_steps": sched.stats.ahead_steps, "preemptions": sched.stats.preemptions,
-            "portion": 512, "temperature": 0.8, "page_tokens": PAGE, "dtype": "bf16", "data": "synthetic ids, random weights"}
+            "portion": _opt(args, "portion", 512), "temperature": temperature, "page_tokens": PAGE,
+            "dtype": _opt(args, "dtype", "bfloat16"), "data": "synthetic ids, random weights"}
 
 
 def mixed32b(args) -> dict:
     from .engine.scheduler import Scheduler
     from .sampling import SamplingParams
     rng = np.random.default_rng(4)
-    ctx, new_len, new = 6000, 1024, 64
+    ctx, new_len, new = _opt(args, "context", 6000), _opt(args, "new_prompt", 1024), _opt(args, "new_tokens", 64)
     # the old requests decode one token while the prompts are fed and 64 more beside the new requests
     lengths = [ctx + 2 * new + 8] * 8 + [new_len + new] * 8
-    cfg, eng = _engine("mixed32b", args.layers, 4, lengths, max_batch_tokens=4096)
+    cfg, eng = _engine("mixed32b", args.layers, 4, lengths, max_batch_tokens=4096, dtype=_opt(args, "dtype", "bfloat16"))
     greedy = SamplingParams(temperature=0.0)
-    sched = Scheduler(eng, prefill_chunk=1024)
-    old = [sched.submit(rng.integers(0, cfg.vocab_size, ctx - 1).tolist(), new + 1, greedy) for _ in range(8)]
+    sched = Scheduler(eng, prefill_chunk=_opt(args, "portion", 1024))
+    old_prompts = [rng.integers(0, cfg.vocab_size, ctx - 1).tolist() for _ in range(8)]
+    old = [sched.submit(p, new + 1, greedy) for p in old_prompts]
     while len(sched.running) < 8 or not all(r.output for r in sched.running):
         sched.step()                                       # the old requests' prompts, then their first token
     torch.cuda.synchronize()
     counters = {"mixed_steps": 0}
-    fresh = [sched.submit(rng.integers(0, cfg.vocab_size, new_len).tolist(), new, greedy) for _ in range(8)]
+    fresh_prompts = [rng.integers(0, cfg.vocab_size, new_len).tolist() for _ in range(8)]
+    fresh = [sched.submit(p, new, greedy) for p in fresh_prompts]
     steps0, dec0 = sched.stats.steps, sum(len(r.output) for r in sched.running)
     t0 = time.perf_counter()
     _drain(sched, counters)
@@ -111,11 +124,13 @@ def mixed32b(args) -> dict:
     dt = time.perf_counter() - t0
     out = sum(len(sched.finished[i].output) for i in old + fresh) - dec0
     eng.cache.books.audit()
+    if _opt(args, "keep_tokens", False):
+        args.kept = (cfg, old_prompts + fresh_prompts, [list(sched.finished[i].output) for i in old + fresh])
     return {"workload": "mixed32b", "layers": cfg.num_hidden_layers, "layers_full": SHAPES["mixed32b"]["num_hidden_layers"],
             "requests": 16, "decoding_context": ctx, "new_prompt_tokens": 8 * new_len, "generated_tokens": out, "seconds": dt,
             "tokens_per_s": (8 * new_len + out) / dt, "generated_per_s": out / dt, "steps": sched.stats.steps - steps0,
             "mixed_steps": counters["mixed_steps"], "ahead_steps": sched.stats.ahead_steps, "preemptions": sched.stats.preemptions,
-            "page_tokens": PAGE, "dtype": "bf16", "data": "synthetic ids, random weights"}
+            "page_tokens": PAGE, "dtype": _opt(args, "dtype", "bfloat16"), "data": "synthetic ids, random weights"}
 
 
 def main() -> int:

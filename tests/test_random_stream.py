@@ -82,7 +82,17 @@ def test_an_engine_with_a_seed_and_a_written_model_folder_hold_the_same_weights(
     write_random_model(folder, cfg, seed=2, std=0.03, norm_std=0.1, dtype=torch.bfloat16)
     from_seed = Engine(config=cfg, random_seed=2, random_std=0.03, random_norm_std=0.1, dtype="bfloat16", max_tokens=64, max_requests=1)
     from_file = Engine(folder, dtype="bfloat16", max_tokens=64, max_requests=1)
-    a, b = from_seed.model, from_file.model
+    _same_weights(from_seed.model, from_file.model)
+    # the same folder under a 32-bit engine: the seed's values rounded to bfloat16, held in 32-bit
+    wide_seed = Engine(config=cfg, random_seed=2, random_std=0.03, random_norm_std=0.1, random_dtype="bfloat16", dtype="float32",
+                       max_tokens=64, max_requests=1)
+    wide_file = Engine(folder, dtype="float32", max_tokens=64, max_requests=1)
+    assert wide_seed.model.embedding.table.dtype == torch.float32
+    _same_weights(wide_seed.model, wide_file.model)
+    assert torch.equal(wide_seed.model.embedding.table, from_seed.model.embedding.table.float())
+
+
+def _same_weights(a, b):
     assert torch.equal(a.embedding.table, b.embedding.table) and torch.equal(a.head.weight, b.head.weight)
     for la, lb in zip(a.layers, b.layers):
         assert torch.equal(la.mixer.w_qkv, lb.mixer.w_qkv) and torch.equal(la.feed_forward.w_down, lb.feed_forward.w_down)

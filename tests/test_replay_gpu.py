@@ -99,6 +99,50 @@ def test_replay_matches_plain(tmp_path_factory, which, dtype, family):
     compare(got, ref, seqs, dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which,page_tokens", [("D", 12), ("E", 12), ("B", 12), ("D", 1), ("A", 1), ("C", 1), ("G", 3)])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed", "mixed_tight"])
+def test_replay_with_pages_that_are_no_power_of_two_and_pages_of_one_token(tmp_path_factory, which, page_tokens, dtype, family):
+    """The engine takes any page size from one token up: a page of 12 tokens puts page edges where no 64-key tile and
+    no 16-byte group ends, a page of one token makes every key a page of its own (the block table is as long as
+    the context).  Same requests, same plain logits."""
+    from hk_b200.engine import Engine
+    d, seqs, ref = setup_case(tmp_path_factory, which, dtype)
+    steps = families(seqs)[family]
+    max_tokens = helpers.peak_tokens(steps, quantum=max(64, page_tokens))
+    engine = Engine(d, dtype=dtype, max_tokens=max_tokens, page_tokens=page_tokens, max_requests=4, max_context=max_tokens)
+    got = helpers.run_trace_on_engine(engine, steps)
+    engine.cache.books.audit()
+    assert all(f == engine.cache.num_pages for f in engine.free_pages()), "pages were not all given back"
+    compare(got, ref, seqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("which,page_tokens", [("D", 16), ("E", 32), ("B", 8)])
+def test_replay_mixed_with_twelve_live_requests(tmp_path_factory, which, page_tokens, dtype):
+    """Up to twelve live requests: steps that mix portions of several prompts with decoded tokens of many others,
+    pure decode steps of 9 to 12 rows (captured graphs of 16 rows, filled up with repeats of the last row), pages
+    that come back and are used again; every position against the plain implementation, in both precisions."""
+    from hk_b200.engine import Engine
+    d, _, _ = setup_case(tmp_path_factory, which, dtype)
+    cfg, weights = helpers.load_plain(d)
+    rng = np.random.default_rng(21)
+    lengths = [int(n) for n in rng.integers(18, 90, 16)]
+    seqs = {f"m{i}": p for i, p in enumerate(helpers.prompts_for(which, rng, lengths))}
+    ref = {rid: plain_qwen3.forward(cfg, weights, ids) for rid, ids in seqs.items()}
+    steps = helpers.trace_mixed(seqs, np.random.default_rng(5), max_live=12, prefill_chunks=(13, 5, 2, 29, 8), decode_tail=20)
+    decode_rows = [len(st["entries"]) for st in steps if all(len(t) == 1 for _, t, _ in st["entries"])]
+    assert max(len(st["entries"]) for st in steps) >= 10 and any(9 <= n <= 12 for n in decode_rows)
+    max_tokens = helpers.peak_tokens(steps)
+    engine = Engine(d, dtype=dtype, max_tokens=max_tokens, page_tokens=page_tokens, max_requests=12, max_context=128)
+    got = helpers.run_trace_on_engine(engine, steps)
+    engine.cache.books.audit()
+    assert all(f == engine.cache.num_pages for f in engine.free_pages())
+    if engine.decode_graphs:
+        assert 16 in engine._graphs
+    compare(got, ref, seqs, dtype)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(tmp_path_factory, tmp_path, dtype):
     """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and `done` lines out."""
