@@ -5,7 +5,12 @@ Keys and defaults follow the reference's reading of a Hugging Face folder
 `num_key_value_heads` defaults to the head count, `head_dim` to hidden/heads,
 `rms_norm_eps` to 1e-6, `rope_theta` to 10000, `max_position_embeddings` to 4096,
 `partial_rotary_factor` to 1, `tie_word_embeddings` to false; `hidden_act` must be
-silu, `mlp_bias`/`attention_bias` must be off, rope scaling must be the default kind.
+silu, `mlp_bias`/`attention_bias` must be off.  `rope_scaling` may be absent or of type
+default, linear, llama3 or yarn with the parameters the reference's engine reads
+(src/engine/config.zig:42-62,163-223: factor at least 1, the original context length
+defaulting to `max_position_embeddings`, llama3's low/high frequency factors, yarn's beta_fast,
+beta_slow and attention factor); any other type is refused, since wrong positions give
+plausible but worse output.
 
 One step beyond the reference: it refuses a sliding window in use
 (src/convert/hf.zig:256-262, src/engine/config.zig:271-279); here `use_sliding_window`
@@ -42,6 +47,7 @@ class Qwen3Config(ModelConfig):
     layer_types: List[str] = field(default_factory=list)
     eos_token_ids: List[int] = field(default_factory=list)
     initializer_range: float = 0.02
+    rope_scaling: Optional[dict] = None      # kind, factor, orig_ctx, ... as `parts.RopeScaling` takes them
 
     # -- derived sizes -----------------------------------------------------------------
     @property
@@ -73,10 +79,23 @@ class Qwen3Config(ModelConfig):
         if opt_bool(raw, "attention_bias", False):
             raise ConfigError("config.json 'attention_bias' = true is not supported for Qwen3")
         rs = raw.get("rope_scaling")
+        scaling = None
         if isinstance(rs, dict):
-            kind = rs.get("rope_type", rs.get("type", "default"))
-            if kind != "default":
-                raise ConfigError(f"config.json 'rope_scaling' of type {kind!r} is not supported (only 'default')")
+            kind = rs.get("rope_type", rs.get("type"))
+            if kind is None and rs.get("factor") is not None:
+                kind = "linear"           # a factor without a type has always meant linear (src/engine/config.zig:183-186)
+            if kind not in (None, "default", "none", "linear", "llama3", "yarn"):
+                raise ConfigError(f"config.json 'rope_scaling' of type {kind!r} is not supported "
+                                  "(supported: default, linear, llama3, yarn)")
+            if kind in ("linear", "llama3", "yarn"):
+                if rs.get("factor") is None:
+                    raise ConfigError(f"config.json 'rope_scaling' of type '{kind}' needs a 'factor'")
+                scaling = {"kind": kind, "factor": float(rs["factor"])}
+                for src, dst, conv in (("original_max_position_embeddings", "orig_ctx", int), ("low_freq_factor", "low_freq_factor", float),
+                                       ("high_freq_factor", "high_freq_factor", float), ("beta_fast", "beta_fast", float),
+                                       ("beta_slow", "beta_slow", float), ("attention_factor", "attn_factor", float)):
+                    if rs.get(src) is not None:
+                        scaling[dst] = conv(rs[src])
         elif rs is not None:
             raise ConfigError(f"config.json 'rope_scaling' = {rs!r} is not an object")
 
@@ -133,10 +152,20 @@ class Qwen3Config(ModelConfig):
         else:
             eos_ids = [int(eos)]
 
+        max_pos = opt_int(raw, "max_position_embeddings", 4096)
+        if scaling is not None:
+            scaling.setdefault("orig_ctx", max_pos)
+            from ..parts.position import RopeScaling
+            try:
+                RopeScaling(**scaling)
+            except ValueError as e:
+                raise ConfigError(f"config.json 'rope_scaling' = {rs!r}: {e}") from None
+
         return cls(
+            rope_scaling=scaling,
             architecture=arch, hidden_size=hidden, num_hidden_layers=layers, intermediate_size=ffn,
             num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, vocab_size=vocab,
-            max_position_embeddings=opt_int(raw, "max_position_embeddings", 4096),
+            max_position_embeddings=max_pos,
             rms_norm_eps=eps, rope_theta=theta, partial_rotary_factor=prf,
             tie_word_embeddings=opt_bool(raw, "tie_word_embeddings", False),
             use_sliding_window=use_window, sliding_window=window, layer_types=layer_types,
@@ -165,6 +194,10 @@ class Qwen3Config(ModelConfig):
             "sliding_window": self.sliding_window,
             "initializer_range": self.initializer_range,
         }
+        if self.rope_scaling:
+            r = self.rope_scaling
+            names = {"orig_ctx": "original_max_position_embeddings", "attn_factor": "attention_factor"}
+            d["rope_scaling"] = {"rope_type": r["kind"], **{names.get(k, k): v for k, v in r.items() if k != "kind"}}
         if self.layer_types:
             d["layer_types"] = list(self.layer_types)
         if self.eos_token_ids:

@@ -209,6 +209,8 @@ HK_API int hk_rms_norm(const float* x, const float* w, const int* rows, void* ou
 //            the first `rot` dims by the token's position, stored to q_out[n, H*hd];
 //   k heads: the same with the key norm weight, stored into the token's cache page;
 //   v heads: stored into the cache page unchanged.
+// `bias` (or null) [(H + 2G) * hd] is added to the projection output first.  `pairing` 0 rotates dims
+// (i, i + rot/2) ("rotate-half"), 1 rotates dims (2i, 2i + 1) ("adjacent"); both read angle i of the tables.
 // Page of a token: block_table[slot_of_token[t]][pos / page_tokens]; the cache layout is
 // [page][G][page_tokens][hd].  With write_kv == 0 only q is produced (a layer that reads
 // another layer's cache).
@@ -222,7 +224,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
-    int write_kv) {
+    int write_kv, const float* __restrict__ bias, int pairing) {
   __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
   pdl_launch_dependents();
   pdl_wait();
@@ -237,6 +239,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
   float ss = 0.f;
   for (int i = lane; i < hd; i += 32) {
     float a = src[i];
+    if (bias) a += bias[(size_t)hh * hd + i];
     v[i] = a;
     ss = fmaf(a, a, ss);
   }
@@ -256,10 +259,11 @@ __global__ void qk_norm_rope_kv_write_kernel(
       const float* c = cos_t + (size_t)pos * half;
       const float* s = sin_t + (size_t)pos * half;
       for (int i = lane; i < half; i += 32) {
-        float a = v[i], b = v[i + half];
+        const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+        float a = v[ia], b = v[ib];
         float ci = c[i], si = s[i];
-        v[i] = a * ci - b * si;
-        v[i + half] = a * si + b * ci;
+        v[ia] = a * ci - b * si;
+        v[ib] = a * si + b * ci;
       }
       __syncwarp();
     }
@@ -289,7 +293,7 @@ qk_norm_rope_kv_write_vec_kernel(
     const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
-    int write_kv) {
+    int write_kv, const float* __restrict__ bias, int pairing) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -302,6 +306,10 @@ qk_norm_rope_kv_write_vec_kernel(
   const bool active = d0 < hd;
   const float* src = qkv + (size_t)t * (H + 2 * G) * hd + (size_t)hh * hd;
   float4 v = active ? *reinterpret_cast<const float4*>(src + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
+  if (bias && active) {
+    const float4 b = *reinterpret_cast<const float4*>(bias + (size_t)hh * hd + d0);
+    v = make_float4(v.x + b.x, v.y + b.y, v.z + b.z, v.w + b.w);
+  }
   const int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);
   const int pos = positions[t];
   if (kind != 2) {
@@ -315,7 +323,15 @@ qk_norm_rope_kv_write_vec_kernel(
         v = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
       }
     }
-    if (rot > 0) {
+    if (rot > 0 && pairing) {
+      // adjacent pairs: a lane's four dims are the pairs d0/2 and d0/2 + 1, both its own
+      if (d0 < rot) {
+        const int half = rot >> 1;
+        const float2 c = *reinterpret_cast<const float2*>(cos_t + (size_t)pos * half + (d0 >> 1));
+        const float2 sn = *reinterpret_cast<const float2*>(sin_t + (size_t)pos * half + (d0 >> 1));
+        v = make_float4(v.x * c.x - v.y * sn.x, v.x * sn.x + v.y * c.x, v.z * c.y - v.w * sn.y, v.z * sn.y + v.w * c.y);
+      }
+    } else if (rot > 0) {
       const int half = rot >> 1, shift = half >> 2;        // partner lanes are `shift` apart
       const bool low = d0 < half, in_rot = d0 < rot;
       const int partner = low ? lane + shift : lane - shift;
@@ -362,35 +378,48 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
                                     int rot, const int* positions, const int* slot_of_token,
                                     const int* block_table, int table_stride, void* k_pages,
                                     void* v_pages, int n, int H, int G, int hd, int page_tokens,
-                                    int write_kv, void* stream) {
+                                    int write_kv, const float* bias, int pairing, void* stream) {
   if (n <= 0) return 0;
-  if (hd > QKR_MAX_HD || hd < 2 || rot > hd || (rot & 1)) return HK_ERR_UNSUPPORTED;
+  if (hd > QKR_MAX_HD || hd < 2 || rot > hd || (rot & 1) || pairing < 0 || pairing > 1) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   long long items = (long long)n * (H + (write_kv ? 2 * G : 0));
   const bool aligned = ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)q_w |
-                          (uintptr_t)k_w | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0);
+                          (uintptr_t)k_w | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)bias) & 15) == 0);
   if (hd <= 128 && (hd & 3) == 0 && (rot & 7) == 0 && aligned) {
     unsigned vblocks = (unsigned)((items + QKV_WARPS - 1) / QKV_WARPS);
     if (dtype == HK_F32)
       return hk_launch(qk_norm_rope_kv_write_vec_kernel<float>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (float*)q_out,
                        q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
-                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv);
+                       (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
     if (dtype == HK_BF16)
       return hk_launch(qk_norm_rope_kv_write_vec_kernel<bf16>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                        k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
-                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv);
+                       (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
     return HK_ERR_UNSUPPORTED;
   }
   unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
   if (dtype == HK_F32)
     return hk_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (float*)q_out, q_w,
                          k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
-                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv);
+                         (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
   if (dtype == HK_BF16)
     return hk_launch(qk_norm_rope_kv_write_kernel<bf16>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                          k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
-                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv);
+                         (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
   return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- bias
+// out[t, j] += bias[j] for a projection with a bias whose product kernel has no such epilogue.
+__global__ void add_bias_kernel(float* __restrict__ out, const float* __restrict__ bias, long long total, int N) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] += bias[i % N];
+}
+
+HK_API int hk_add_bias(float* out, const float* bias, int n, int N, void* stream) {
+  if (n <= 0 || N <= 0) return 0;
+  long long total = (long long)n * N;
+  return hk_launch(add_bias_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, out, bias, total, N);
 }
 
 // ----------------------------------------------------------------------------- swiglu

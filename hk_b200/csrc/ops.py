@@ -196,12 +196,23 @@ def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, bloc
 # ---- per-head norm + rotation + cache write ---------------------------------------------
 
 
+PAIRINGS = {"half": 0, "adjacent": 1}
+
+
 def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_dim, positions,
                           slot_of_token, block_table, k_pages, v_pages, n_heads, n_kv_heads, head_dim,
-                          page_tokens, write_kv=True) -> None:
+                          page_tokens, write_kv=True, bias=None, pairing="half") -> None:
     """Splits the fused projection qkv[n, (H+2G)*hd] (float32): q heads are normalised (if
     q_weight), rotated (if rotary_dim > 0) and stored to q_out[n, H*hd]; k heads likewise and
-    stored, with the v heads, into the token's cache page [page, G, page_tokens, hd]."""
+    stored, with the v heads, into the token's cache page [page, G, page_tokens, hd].
+    `bias` (float32 [(H+2G)*hd]) is added to the projection first.  `pairing`: "half" rotates dims
+    (i, i + rotary_dim/2), "adjacent" dims (2i, 2i+1)."""
+    if pairing not in PAIRINGS:
+        raise KernelError(f"qk_norm_rope_kv_write: pairing {pairing!r} is neither 'half' nor 'adjacent'")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != (n_heads + 2 * n_kv_heads) * head_dim:
+            raise KernelError("qk_norm_rope_kv_write: bias must have (H + 2G) * head_dim entries")
     _need(qkv, "qkv", torch.float32, 2)
     _need(q_out, "q_out", dims=2)
     n = qkv.shape[0]
@@ -234,16 +245,32 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
         _ptr(cos if rotary_dim > 0 else None), _ptr(sin if rotary_dim > 0 else None), int(rotary_dim),
         _ptr(positions), _ptr(slot_of_token), _ptr(block_table if write_kv else None),
         int(block_table.shape[1]) if write_kv else 0, _ptr(k_pages if write_kv else None),
-        _ptr(v_pages if write_kv else None), n, H, G, hd, int(page_tokens), 1 if write_kv else 0, _stream()),
+        _ptr(v_pages if write_kv else None), n, H, G, hd, int(page_tokens), 1 if write_kv else 0, _ptr(bias),
+        PAIRINGS[pairing], _stream()),
         "qk_norm_rope_kv_write")
 
 
 # ---- matrix product -------------------------------------------------------------------
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    """out[M, N] (float32) = a[M, K] @ w[N, K]^T (+ out when `accumulate`).
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """out[t, :] += bias (both float32)."""
+    _need(out, "out", torch.float32, 2)
+    _need(bias, "bias", torch.float32, 1)
+    if bias.shape[0] != out.shape[1]:
+        raise KernelError("add_bias: one bias entry per output column")
+    lib = build.load("elementwise")
+    _check(lib.hk_add_bias(_ptr(out), _ptr(bias), out.shape[0], out.shape[1], _stream()), "add_bias")
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+         bias: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] (float32) = a[M, K] @ w[N, K]^T (+ out when `accumulate`) (+ bias[N], float32).
     a and w share a type: float32 (plain FMA) or bfloat16 (fp32 accumulation)."""
+    if bias is not None:
+        gemm(a, w, out, accumulate)
+        add_bias(out, bias)
+        return
     _need(a, "a", dims=2)
     _need(w, "w", dims=2)
     _need(out, "out", torch.float32, 2)

@@ -10,14 +10,15 @@ or the full attention mixer.
 from __future__ import annotations
 
 from ..config import Qwen3Config, register_architecture
-from ..parts import (GQAAttention, OutputHead, PreNormBlock, RMSNorm, RotaryEmbedding, SwiGLUFeedForward,
+from ..parts import (GQAAttention, OutputHead, PreNormBlock, RMSNorm, RopeScaling, RotaryEmbedding, SwiGLUFeedForward,
                      TokenEmbedding)
 from .spec import ModelSpec
 
 
 def build_qwen3(cfg: Qwen3Config, max_positions: int = 0) -> ModelSpec:
     positions = max_positions or cfg.max_position_embeddings
-    rope = RotaryEmbedding(cfg.rope_theta, cfg.rotary_dim, positions)
+    scaling = RopeScaling(**cfg.rope_scaling) if cfg.rope_scaling else None
+    rope = RotaryEmbedding(cfg.rope_theta, cfg.rotary_dim, positions, pairing="half", scaling=scaling)
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."

@@ -5,10 +5,10 @@ from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .feed_forward import SwiGLUFeedForward
 from .norm import RMSNorm
-from .position import RotaryEmbedding
+from .position import RopeScaling, RotaryEmbedding
 
 __all__ = [
     "GQAAttention", "KVCacheSpec", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
-    "RMSNorm", "RotaryEmbedding", "StateSpec", "StepTables", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
+    "RMSNorm", "RopeScaling", "RotaryEmbedding", "StateSpec", "StepTables", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
     "part_class", "register_part",
 ]

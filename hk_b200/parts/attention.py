@@ -10,7 +10,8 @@ Steps, in the reference's order (src/engine/cpu_backend.zig:266-304):
   (src/engine/attention.zig:45-103), q head h reading kv head h // (H/G) (attention.zig:56)
   residual += att Wo^T (cpu_backend.zig:303-304)
 
-Sizes, the norm's eps, the position encoding, the window and the scale are parameters.  The
+Sizes, the norm's eps, the position encoding (with its pairing of dims), the window, the scale and
+biases on the projections are parameters.  The
 reference's attention has no window (src/engine/config.zig:271-279 refuses one); `window=w`
 limits the keys of position p to (p - w, p] and lets the cache give pages back.
 """
@@ -31,7 +32,8 @@ class GQAAttention(Part):
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
                  qk_norm_eps: Optional[float] = None, position: Optional[RotaryEmbedding] = None,
-                 window: Optional[int] = None, scale: Optional[float] = None):
+                 window: Optional[int] = None, scale: Optional[float] = None, qkv_bias: bool = False,
+                 o_bias: bool = False):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
         if head_dim > 256 or head_dim < 2:
@@ -44,6 +46,9 @@ class GQAAttention(Part):
         self.position = position
         self.window = window
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        # biases on the projections: the reference turns `qkv_bias` on by architecture (src/engine/config.zig:313)
+        self.qkv_bias, self.o_bias = bool(qkv_bias), bool(o_bias)
+        self.b_qkv = self.b_o = None
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
         self._tables_key = None        # set at bind: the flash kernels' work items, when they take these sizes
         self._sm_count = 0
@@ -63,6 +68,12 @@ class GQAAttention(Part):
         if self.qk_norm_eps is not None:
             specs[p + "q_norm.weight"] = ParamSpec((hd,), VECTOR, "one_plus_normal")
             specs[p + "k_norm.weight"] = ParamSpec((hd,), VECTOR, "one_plus_normal")
+        if self.qkv_bias:
+            specs[p + "q_proj.bias"] = ParamSpec((H * hd,), VECTOR)
+            specs[p + "k_proj.bias"] = ParamSpec((G * hd,), VECTOR)
+            specs[p + "v_proj.bias"] = ParamSpec((G * hd,), VECTOR)
+        if self.o_bias:
+            specs[p + "o_proj.bias"] = ParamSpec((d,), VECTOR)
         return specs
 
     def cache_spec(self):
@@ -74,6 +85,10 @@ class GQAAttention(Part):
         wide = torch.float32 if any(t.dtype == torch.float32 for t in qkv) else qkv[0].dtype    # one kept in 32-bit: all are
         self.w_qkv = torch.cat([t.to(wide) for t in qkv], dim=0).contiguous()
         self.w_o = tensors[p + "o_proj.weight"]
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors[p + f"{n}_proj.bias"] for n in "qkv"]).contiguous()
+        if self.o_bias:
+            self.b_o = tensors[p + "o_proj.bias"]
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[p + "q_norm.weight"]
             self.k_norm = tensors[p + "k_norm.weight"]
@@ -123,17 +138,20 @@ class GQAAttention(Part):
         q = torch.empty((n, H * hd), dtype=xb.dtype, device=xb.device)
         cos = sin = None
         rot = 0
+        pairing = "half"
         if self.position is not None:
             cos, sin, rot = self.position.tables()
+            pairing = getattr(self.position, "pairing", "half")
+        # the projections' bias rides on the fused kernel's load
         ops.qk_norm_rope_kv_write(
             qkv, q, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, cos, sin, rot, ctx.positions,
             ctx.slot_of_token, cache.block_table, cache.k_pages, cache.v_pages, H, G, hd, cache.page_tokens,
-            write_kv=write_cache)
+            write_kv=write_cache, bias=self.b_qkv, pairing=pairing)
         att = torch.empty_like(q)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
                             att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
                             plan=plan)
-        ops.gemm(att, self.w_o, residual, accumulate=True)
+        ops.gemm(att, self.w_o, residual, accumulate=True, bias=self.b_o)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -47,6 +47,66 @@ def rope_inv_freq(theta: float, rotary_dim: int) -> np.ndarray:
     return np.power(np.float64(theta), -(2.0 * i) / np.float64(rotary_dim)).astype(np.float32)
 
 
+def rope_inv_freq_scaled(theta: float, rotary_dim: int, kind: str, factor: float = 1.0, orig_ctx: int = 0,
+                         low_freq_factor: float = 1.0, high_freq_factor: float = 4.0, beta_fast: float = 32.0,
+                         beta_slow: float = 1.0) -> np.ndarray:
+    """Frequencies stretched for longer contexts (src/engine/ops.zig:96-144), every step in float64:
+    linear: inv / factor; llama3: by wavelength against orig_ctx / high and orig_ctx / low with a blended
+    band; yarn: a ramp between the dims that make beta_fast and beta_slow rotations in orig_ctx."""
+    n = float(rotary_dim)
+    out = np.zeros(rotary_dim // 2, dtype=np.float64)
+    low = high = 0.0
+    if kind == "yarn":
+        corr = lambda rot: n * np.log(orig_ctx / (rot * 2.0 * np.pi)) / (2.0 * np.log(theta))
+        low = max(0.0, np.floor(corr(beta_fast)))
+        high = min(n - 1.0, np.ceil(corr(beta_slow)))
+        if low == high:
+            high += 0.001
+    for i in range(rotary_dim // 2):
+        inv = float(theta) ** (-(2.0 * i) / n)
+        if kind == "none":
+            v = inv
+        elif kind == "linear":
+            v = inv / factor
+        elif kind == "llama3":
+            wavelen = 2.0 * np.pi / inv
+            if wavelen < orig_ctx / high_freq_factor:
+                v = inv
+            elif wavelen > orig_ctx / low_freq_factor:
+                v = inv / factor
+            else:
+                smooth = (orig_ctx / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor)
+                v = (1.0 - smooth) * inv / factor + smooth * inv
+        elif kind == "yarn":
+            ramp = min(1.0, max(0.0, (i - low) / (high - low)))
+            v = (inv / factor) * ramp + inv * (1.0 - ramp)
+        else:
+            raise ValueError(kind)
+        out[i] = v
+    return out.astype(np.float32)
+
+
+def rope_mscale(kind: str, factor: float = 1.0, attn_factor: float = 1.0) -> float:
+    """Only yarn changes the magnitude: attn_factor * (0.1 ln(factor) + 1) (src/engine/ops.zig:146-151)."""
+    return float(np.float32(attn_factor) * np.float32(1.0 + 0.1 * np.log(factor))) if kind == "yarn" else 1.0
+
+
+def rope_rotate_adjacent(x: np.ndarray, head_dim: int, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """The `.norm` style: pairs (2i, 2i + 1) over the first 2*len(cos) dims of every head
+    (src/engine/ops.zig:166-172)."""
+    t, width = x.shape
+    heads = width // head_dim
+    half = cos.shape[1]
+    xr = x.reshape(t, heads, head_dim).copy()
+    a = xr[:, :, 0:2 * half:2].copy()
+    b = xr[:, :, 1:2 * half:2].copy()
+    c = cos[:, None, :].astype(x.dtype)
+    s = sin[:, None, :].astype(x.dtype)
+    xr[:, :, 0:2 * half:2] = a * c - b * s
+    xr[:, :, 1:2 * half:2] = a * s + b * c
+    return xr.reshape(t, width)
+
+
 def rope_angles(positions, inv_freq: np.ndarray):
     """a = f32(pos) * inv_freq[i] in float32; cos and sin of that float32 angle
     (src/engine/ops.zig:154-161; mscale is 1 without YaRN, ops.zig:146-151)."""

@@ -38,12 +38,17 @@ def gemm(a, w, out0=None):
     return y if out0 is None else y + out0.double()
 
 
-def qk_norm_rope(qkv, q_weight, k_weight, eps, cos, sin, rotary_dim, positions, H, G, hd):
-    """Per-head norm then rotate-half rotation of the q and k heads of qkv[n, (H+2G)*hd]
-    (src/engine/ops.zig:32-38,176-181; order: src/kernels_impl.zig:55-66).
-    Returns q[n, H, hd], k[n, G, hd], v[n, G, hd] in float64."""
+def qk_norm_rope(qkv, q_weight, k_weight, eps, cos, sin, rotary_dim, positions, H, G, hd, bias=None, pairing="half"):
+    """Per-head norm then rotation of the q and k heads of qkv[n, (H+2G)*hd]
+    (src/engine/ops.zig:32-38; order: src/kernels_impl.zig:55-66); the rotation pairs dims
+    (i, i + half) ("half", the reference's .neox) or (2i, 2i + 1) ("adjacent", its .norm):
+    src/engine/ops.zig:164-181.  A bias is added to the projection first (cf. qkv_bias,
+    src/engine/config.zig:313).  Returns q[n, H, hd], k[n, G, hd], v[n, G, hd] in float64."""
     n = qkv.shape[0]
-    x = qkv.double().reshape(n, H + 2 * G, hd)
+    x = qkv.double()
+    if bias is not None:
+        x = x + bias.double()[None, :]
+    x = x.reshape(n, H + 2 * G, hd)
     q, k, v = x[:, :H].clone(), x[:, H:H + G].clone(), x[:, H + G:].clone()
 
     def norm(t, w):
@@ -57,8 +62,13 @@ def qk_norm_rope(qkv, q_weight, k_weight, eps, cos, sin, rotary_dim, positions, 
         half = rotary_dim // 2
         c = cos.double()[positions.long()][:, None, :]
         s = sin.double()[positions.long()][:, None, :]
-        a, b = t[..., :half].clone(), t[..., half:2 * half].clone()
         t = t.clone()
+        if pairing == "adjacent":
+            a, b = t[..., 0:2 * half:2].clone(), t[..., 1:2 * half:2].clone()
+            t[..., 0:2 * half:2] = a * c - b * s
+            t[..., 1:2 * half:2] = a * s + b * c
+            return t
+        a, b = t[..., :half].clone(), t[..., half:2 * half].clone()
         t[..., :half] = a * c - b * s
         t[..., half:2 * half] = a * s + b * c
         return t

@@ -51,7 +51,11 @@ def test_window_layers_from_layer_types_and_max_window_layers():
     ({"hidden_act": "gelu"}, "hidden_act"),
     ({"mlp_bias": True}, "mlp_bias"),
     ({"attention_bias": True}, "attention_bias"),
-    ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"rope_scaling": {"rope_type": "dynamic", "factor": 4.0}}, "rope_scaling"),
+    ({"rope_scaling": {"rope_type": "yarn"}}, "factor"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 0.5}}, "rope_scaling"),
+    ({"rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 4.0, "high_freq_factor": 1.0}}, "low_freq_factor"),
+    ({"rope_scaling": "yarn"}, "rope_scaling"),
     ({"num_key_value_heads": 3}, "num_key_value_heads"),
     ({"head_dim": 258}, "head_dim"),
     ({"head_dim": 15}, "head_dim"),
@@ -69,6 +73,21 @@ def test_bad_values_name_the_key(change, needle):
     with pytest.raises(ConfigError) as e:
         config_from_dict(raw)
     assert needle in str(e.value)
+
+
+def test_rope_scaling_kinds_are_read_with_the_reference_defaults():
+    raw = dict(helpers.TINY_B, rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64})
+    c = config_from_dict(raw)
+    assert c.rope_scaling == {"kind": "yarn", "factor": 4.0, "orig_ctx": 64}
+    assert config_from_dict(c.to_dict()).rope_scaling == c.rope_scaling
+    c = config_from_dict(dict(helpers.TINY_B, rope_scaling={"factor": 2.0}))                 # a factor alone means linear
+    assert c.rope_scaling["kind"] == "linear"
+    c = config_from_dict(dict(helpers.TINY_B, rope_scaling={"rope_type": "llama3", "factor": 8.0}))
+    assert c.rope_scaling["orig_ctx"] == helpers.TINY_B["max_position_embeddings"]         # defaults to the training context
+    assert config_from_dict(dict(helpers.TINY_B, rope_scaling={"rope_type": "default"})).rope_scaling is None
+    from hk_b200.models.qwen3 import build_qwen3
+    rope = build_qwen3(config_from_dict(raw), 32).layers[0].mixer.position
+    assert rope.scaling.kind == "yarn" and rope.pairing == "half"
 
 
 def test_registry_names_what_it_supports():

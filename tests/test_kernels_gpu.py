@@ -189,6 +189,60 @@ def test_qk_norm_rope_kv_write_many_tokens(dtype, H, G, hd, pt, rot, norm, ntok)
     close(vp, rv, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("H,G,hd,pt,rot", [(4, 2, 16, 4, 16), (5, 1, 48, 16, 24), (8, 8, 128, 16, 128), (3, 1, 40, 8, 24), (2, 1, 24, 4, 22),
+                                            (4, 2, 160, 16, 160), (6, 2, 64, 16, 32)])
+@pytest.mark.parametrize("pairing,with_bias", [("adjacent", False), ("adjacent", True), ("half", True)])
+def test_qk_norm_rope_kv_write_with_bias_and_adjacent_pairs(dtype, H, G, hd, pt, rot, pairing, with_bias):
+    # both kernels (a lane with four consecutive dims; a warp over shared memory for the other sizes), a bias on
+    # the projection, and the rotation of dims (2i, 2i + 1) instead of (i, i + half)
+    rng = np.random.default_rng(H * hd + pt + rot)
+    lens = [9, 30, 17]
+    k_pages, v_pages, bt, _, _ = make_paged(rng, 3, lens, G, hd, pt, dtype)
+    k_pages.zero_()
+    v_pages.zero_()
+    slot = torch.tensor([1] * 18 + [0] + [2] * 3, dtype=torch.int32)
+    pos = torch.tensor(list(range(12, 30)) + [8] + [14, 15, 16], dtype=torch.int32)
+    n = slot.numel()
+    qkv = torch.from_numpy(rng.standard_normal((n, (H + 2 * G) * hd))).float() * 2
+    bias = torch.from_numpy(rng.standard_normal((H + 2 * G) * hd)).float() if with_bias else None
+    qw = (1 + 0.2 * torch.from_numpy(rng.standard_normal(hd))).float()
+    kw = (1 + 0.2 * torch.from_numpy(rng.standard_normal(hd))).float()
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * torch.from_numpy(rng.uniform(0.001, 1.0, rot // 2))[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    q_out = torch.empty(n, H * hd, dtype=dtype, device=DEV)
+    kp, vp = k_pages.to(DEV), v_pages.to(DEV)
+    ops().qk_norm_rope_kv_write(qkv.to(DEV), q_out, qw.to(DEV), kw.to(DEV), 1e-5, cos.to(DEV), sin.to(DEV), rot, pos.to(DEV),
+                                slot.to(DEV), bt.to(DEV), kp, vp, H, G, hd, pt, bias=None if bias is None else bias.to(DEV),
+                                pairing=pairing)
+    q, k, v = ref_ops.qk_norm_rope(qkv, qw, kw, 1e-5, cos, sin, rot, pos, H, G, hd, bias=bias, pairing=pairing)
+    close(q_out, q.reshape(n, H * hd), dtype)
+    rk, rv = torch.zeros_like(k_pages, dtype=torch.float64), torch.zeros_like(v_pages, dtype=torch.float64)
+    ref_ops.write_pages(k, v, rk, rv, bt, slot, pos, pt)
+    close(kp, rk, dtype)
+    close(vp, rv, dtype)
+
+
+def test_adjacent_rotation_reference_fact():
+    # src/engine/ops.zig:236-252, the `.norm` style: 90 degrees on pairs (x0,x1),(x2,x3): [1,0,0,1] -> [0,1,-1,0]
+    qkv = torch.tensor([[1.0, 0, 0, 1] + [0.0] * 8], device=DEV)
+    q_out = torch.empty(1, 4, dtype=torch.float32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kp = torch.zeros(1, 1, 1, 4, device=DEV)
+    ops().qk_norm_rope_kv_write(qkv, q_out, None, None, 0.0, torch.zeros(1, 2, device=DEV), torch.ones(1, 2, device=DEV),
+                                4, z, z, torch.zeros(1, 1, dtype=torch.int32, device=DEV), kp, kp.clone(), 1, 1, 4, 1, pairing="adjacent")
+    assert torch.allclose(q_out.cpu(), torch.tensor([[0.0, 1, -1, 0]]), atol=1e-6)
+
+
+@pytest.mark.parametrize("n,N", [(1, 7), (33, 4096), (5, 1001)])
+def test_add_bias(n, N):
+    out0 = torch.randn(n, N, device=DEV)
+    bias = torch.randn(N, device=DEV)
+    out = out0.clone()
+    ops().add_bias(out, bias)
+    assert torch.equal(out, out0 + bias[None, :])
+
+
 def test_rotation_reference_fact():
     # src/engine/ops.zig:236-252: 90 degrees in the half-split pairing: [1,0,0,1] -> [0,-1,1,0]
     qkv = torch.tensor([[1.0, 0, 0, 1] + [0.0] * 8], device=DEV)

@@ -67,6 +67,11 @@ def test_rms_norm_part(dtype):
     out = torch.empty(11, 72, dtype=dtype, device="cuda")
     part.forward(x, out)
     np.testing.assert_allclose(out.double().cpu().numpy(), P.rms_norm(x.double().cpu().numpy(), w["n.weight"], 3e-6), **tol(dtype))
+    # a checkpoint that stores weight - 1: the offset is a parameter of the part
+    shifted = RMSNorm(72, 3e-6, "n.weight", weight_offset=1.0)
+    prec, w = bind_random(shifted, dtype)
+    shifted.forward(x, out)
+    np.testing.assert_allclose(out.double().cpu().numpy(), P.rms_norm(x.double().cpu().numpy(), w["n.weight"] + 1.0, 3e-6), **tol(dtype))
 
 
 def test_rotary_tables_match_the_plain_angles():
@@ -95,25 +100,40 @@ def test_swiglu_feed_forward_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("window,qk_norm,rope", [(None, True, True), (7, True, True), (None, False, False)])
-def test_attention_part_whole_then_cut(dtype, window, qk_norm, rope):
+@pytest.mark.parametrize("window,qk_norm,rope,bias,pairing,scaling", [
+    (None, True, True, False, "half", None), (7, True, True, False, "half", None), (None, False, False, False, "half", None),
+    (None, True, True, True, "adjacent", None), (5, False, True, True, "half", dict(kind="yarn", factor=4.0, orig_ctx=16)),
+    (None, True, True, False, "adjacent", dict(kind="llama3", factor=8.0, orig_ctx=32)),
+    (None, False, True, True, "half", dict(kind="linear", factor=2.0))])
+def test_attention_part_whole_then_cut(dtype, window, qk_norm, rope, bias, pairing, scaling):
     """The attention mixer alone: a whole sequence in one step equals the plain functions, and the
-    same sequence cut into a portion and single tokens gives the same rows."""
+    same sequence cut into a portion and single tokens gives the same rows.  Its parameters one by one: a
+    window, the per-head norm, the rotation with either pairing of dims and every kind of frequency scaling,
+    biases on the four projections."""
     from hk_b200.cache.device import PagedCache
-    from hk_b200.parts import GQAAttention, RotaryEmbedding
+    from hk_b200.parts import GQAAttention, RopeScaling, RotaryEmbedding
     d, H, G, hd, T = 40, 6, 2, 16, 29
-    pos_part = RotaryEmbedding(5000.0, 8, 64) if rope else None
-    part = GQAAttention(d, H, G, hd, "a.", qk_norm_eps=1e-5 if qk_norm else None, position=pos_part, window=window)
+    pos_part = RotaryEmbedding(5000.0, 8, 64, pairing=pairing, scaling=RopeScaling(**scaling) if scaling else None) if rope else None
+    part = GQAAttention(d, H, G, hd, "a.", qk_norm_eps=1e-5 if qk_norm else None, position=pos_part, window=window,
+                        qkv_bias=bias, o_bias=bias)
     prec, w = bind_random(part, dtype, std=0.2)
     xb = torch.randn(T, d, device="cuda").to(dtype)
     x = xb.double().cpu().numpy()
     q, k, v = (P.linear(x, w[f"a.{n}_proj.weight"]) for n in "qkv")
+    if bias:
+        q, k, v = (t + w[f"a.{n}_proj.bias"][None, :] for t, n in ((q, "q"), (k, "k"), (v, "v")))
     if qk_norm:
         q, k = P.head_norm(q, w["a.q_norm.weight"], hd, 1e-5), P.head_norm(k, w["a.k_norm.weight"], hd, 1e-5)
     if rope:
-        cos, sin = P.rope_angles(np.arange(T), P.rope_inv_freq(5000.0, 8))
-        q, k = P.rope_rotate_half(q, hd, cos, sin), P.rope_rotate_half(k, hd, cos, sin)
+        kind = scaling["kind"] if scaling else "none"
+        sc = {k_: v_ for k_, v_ in (scaling or {}).items() if k_ != "kind"}
+        cos, sin = P.rope_angles(np.arange(T), P.rope_inv_freq_scaled(5000.0, 8, kind, **sc))
+        m = P.rope_mscale(kind, sc.get("factor", 1.0))
+        rotate = P.rope_rotate_half if pairing == "half" else P.rope_rotate_adjacent
+        q, k = rotate(q, hd, cos * m, sin * m), rotate(k, hd, cos * m, sin * m)
     want = P.linear(P.causal_gqa_attention(q, k, v, H, G, hd, window=window), w["a.o_proj.weight"])
+    if bias:
+        want = want + w["a.o_proj.bias"][None, :]
 
     def run(cuts):
         cache = PagedCache([[part.cache_spec()]], prec, 4, 16, 2, 64)

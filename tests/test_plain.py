@@ -28,6 +28,42 @@ def test_inv_freq_facts_of_the_reference():
     assert abs(f[31] / (4.0 * 3.333803761e-05) - 1) < 1e-5
 
 
+# Numbers the reference's own tests carry, exported from Transformers (src/engine/ops.zig:303-329): (index, inv_freq)
+LLAMA3 = [(0, 1.0), (1, 6.636012793e-01), (7, 5.666961893e-02), (8, 3.760603070e-02), (12, 7.292665076e-03),
+          (16, 5.248460220e-04), (20, 3.428102355e-05), (24, 6.647869668e-06), (31, 3.767322596e-07)]
+YARN = [(0, 1.0), (1, 7.498942018e-01), (7, 1.333521456e-01), (8, 1.000000015e-01), (12, 2.797399648e-02),
+        (16, 6.538461894e-03), (20, 1.337886788e-03), (24, 2.500000119e-04), (31, 3.333803761e-05)]
+LINEAR = [(0, 0.25), (1, 1.874735504e-01), (16, 2.499999944e-03), (31, 3.333803761e-05)]
+
+
+def test_rope_scaling_numbers_of_the_reference():
+    """Plain restatement and the engine's rotary part against the values the reference pins (relative 2e-6, as there)."""
+    from hk_b200.parts import RopeScaling, RotaryEmbedding
+    cases = [
+        (LLAMA3, 500000.0, dict(kind="llama3", factor=8.0, orig_ctx=8192, low_freq_factor=1.0, high_freq_factor=4.0)),
+        (YARN, 10000.0, dict(kind="yarn", factor=4.0, orig_ctx=4096)),
+        (LINEAR, 10000.0, dict(kind="linear", factor=4.0)),
+    ]
+    for probes, theta, kw in cases:
+        plain = P.rope_inv_freq_scaled(theta, 64, **kw)
+        part = RotaryEmbedding(theta, 64, 8, scaling=RopeScaling(**kw)).inv_freq().numpy()
+        for i, want in probes:
+            assert abs(plain[i] / want - 1) < 2e-6, (kw["kind"], i)
+            assert abs(part[i] / want - 1) < 2e-6, (kw["kind"], i)
+        assert np.array_equal(plain, part)
+    # magnitude: only yarn changes it (src/engine/ops.zig:318-319)
+    assert abs(P.rope_mscale("yarn", 4.0) / 1.138629436 - 1) < 1e-6
+    assert abs(RotaryEmbedding(10000.0, 64, 8, scaling=RopeScaling("yarn", 4.0, 4096)).mscale() / 1.138629436 - 1) < 1e-6
+    assert P.rope_mscale("llama3", 8.0) == 1.0 and RotaryEmbedding(5e5, 64, 8, scaling=RopeScaling("llama3", 8.0, 8192)).mscale() == 1.0
+    assert np.array_equal(P.rope_inv_freq_scaled(1e4, 64, "none"), P.rope_inv_freq(1e4, 64))
+
+
+def test_adjacent_rotation_fact_of_the_reference():
+    # src/engine/ops.zig:236-252 with style .norm: pairs (x0,x1),(x2,x3) by 90 degrees: [1,0,0,1] -> [0,1,-1,0]
+    out = P.rope_rotate_adjacent(np.array([[1.0, 0.0, 0.0, 1.0]]), 4, np.zeros((1, 2)), np.ones((1, 2)))
+    assert np.allclose(out, [[0, 1, -1, 0]], atol=1e-12)
+
+
 def test_head_norm_shares_one_weight_across_heads():
     rng = np.random.default_rng(0)
     x = rng.standard_normal((3, 8))
