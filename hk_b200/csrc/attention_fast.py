@@ -45,6 +45,12 @@ def tc_prefill_supported(hd: int, group: int) -> bool:
     return hd in (64, 128) and group <= 128
 
 
+def tc2_prefill_supported(hd: int, group: int, page_tokens: int) -> bool:
+    """The tcgen05 kernel with two query tiles per CTA and K/V by TMA: the pages must be whole boxes of a 128-key tile."""
+    boxes = (page_tokens % 8 == 0 and 128 % page_tokens == 0) or (page_tokens > 0 and page_tokens % 128 == 0)
+    return tc_prefill_supported(hd, group) and boxes
+
+
 def split_chunk(span: int, want: int) -> int:
     """Keys per split when `span` keys (counted from a tile boundary) go to `want` splits: whole tiles."""
     return -(-(-(-span // want)) // TILE_N) * TILE_N
@@ -73,7 +79,8 @@ def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window:
     when the kernels do not take this grouping.  `fixed_splits` > 0 forces that many items per run (a shape
     that does not change from step to step, for captured decode graphs); `max_context` then bounds the key
     range any later step can bring, which sizes the kernel's page-id buffer.  `prefill_rows`: rows per CTA for
-    batches with prompt portions: 64 (the mma.sync kernel) or 128 (the tcgen05 kernel, head sizes 64 and 128)."""
+    batches with prompt portions: 64 (the mma.sync kernel), 128 (the tcgen05 kernel, head sizes 64 and 128) or 256
+    (its variant with two query tiles per CTA, which also wants TMA-able pages: `tc2_prefill_supported`)."""
     group = H // G
     nw = 1 if all(l == 1 for l in q_lens) else prefill_rows // 16
     rows = 16 * nw
@@ -103,7 +110,7 @@ def plan_arrays(slots, q_starts, q_lens, start_positions, n_tokens: int, window:
         kv_len = kv_hi - kv_lo
         if fixed_splits > 0:
             want = fixed_splits
-        elif base_ctas >= 2 * sm_count or nw == 8:
+        elif base_ctas >= 2 * sm_count or nw >= 8:
             want = 1
         else:
             want = max(1, min(2 * sm_count // base_ctas, kv_len // 64, 32))
@@ -202,6 +209,19 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
     if plan.n_parts:
         part_o = torch.empty((plan.n_parts, G, rows, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((plan.n_parts, G, rows, 2), dtype=torch.float32, device=q.device)
+    if plan.nw == 16:
+        if plan.n_parts or not tc2_prefill_supported(hd, H // G, int(page_tokens)):
+            return False
+        lib_tc = build.load("attention_prefill_tc")
+        code = lib_tc.hk_attention_prefill_tc2(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), ctypes.c_longlong(k_pages.shape[0]), _ptr(block_table),
+            int(block_table.shape[1]), _ptr(plan.items), plan.n_items, _ptr(out), H, G, hd, int(page_tokens), int(window),
+            ctypes.c_float(scale * math.log2(math.e)), plan.max_keys // int(page_tokens) + 2,
+            _ptr(gemm_fast.status_flag(q.device)), stream)
+        if code == _UNSUPPORTED:
+            return False
+        ops._check(code, "paged_attention (tcgen05 prefill, two query tiles)")
+        return True
     if plan.nw == 8:
         if plan.n_parts or not tc_prefill_supported(hd, H // G):
             return False

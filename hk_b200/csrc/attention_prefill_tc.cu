@@ -1,16 +1,17 @@
 // Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores, for head sizes
 // 64 and 128 (bf16).  One CTA takes one work item (a run of query tokens of one request, with its key range)
 // for one kv head: its 128 rows are (token, query head of the group) pairs, so the group's heads share every
-// K/V tile.  Keys come in tiles of 64 through a ring of four stages (three tiles in flight).  Per tile:
+// K/V tile.  Keys come in tiles of 128 (a product of 128 x 128 x 16 reads 8 KB of shared-memory operands for
+// 0.5 MFLOP and is bound by the tensor pipe; at 64 keys it was bound by the operand reads, and every tile pays
+// one chain of hand-offs whatever its width) through a ring of three K stages and two V stages.  Per tile:
 //
-//   loader warps (4)   warp w owns stage w and every fourth tile: it cp.asyncs the K tile and the V tile from
-//                      wherever the block table says the pages are into shared memory in the 128-byte-swizzled
-//                      layout the tensor core reads ([half of the head][key][128 bytes]); Q is loaded the same
-//                      way once
-//   MMA warp (1 lane)  S = Q K^T   : tcgen05.mma 128 x 64 x 16, Q and K K-major from shared memory, S in
+//   loader warps (4)   together they cp.async the K tile and the V tile from wherever the block table says the
+//                      pages are (any page size) into shared memory in the 128-byte-swizzled layout the tensor
+//                      core reads ([half of the head][key][128 bytes]); Q is loaded the same way once
+//   MMA warp (1 lane)  S = Q K^T   : tcgen05.mma 128 x 128 x 16, Q and K K-major from shared memory, S in
 //                                     tensor memory (two S buffers, so the next tile's scores are computed
 //                                     while this tile's softmax runs)
-//                      O += P V    : tcgen05.mma 128 x HD x 16, P from tensor memory (two buffers of 32
+//                      O += P V    : tcgen05.mma 128 x HD x 16, P from tensor memory (two buffers of 64
 //                                     columns beside S and O: it never passes through shared memory), V MN-major
 //                                     (keys are its K dimension) from shared memory, O in tensor memory
 //   softmax warps (8)  two threads per row (half of the tile's keys each): tcgen05.ld of the S row, mask, running
@@ -24,24 +25,19 @@
 // All hand-offs are mbarriers; every wait is bounded and a time-out makes the CTA set `status`, free its tensor
 // memory and leave without writing.  Reference counterpart: `attention_tc_128`, src/cuda_device.zig:1069-1248
 // (mma.sync, single sequence, contiguous cache).
+#include <cuda.h>
 #include <math_constants.h>
 
-#include "common.cuh"
+#include <mutex>
 
-#ifdef HK_TRACE
-// Timing probes for one CTA (the first, heaviest work item, kv head 0): role r writes clock64() at its n-th probe.
-__device__ long long hk_trace_buf[4][512];
-__device__ int hk_trace_n[4];
-#define TRACE(role) do { if (trace_on) { if (trace_i < 512) { hk_trace_buf[role][trace_i] = clock64(); hk_trace_n[role] = ++trace_i; } } } while (0)
-#else
-#define TRACE(role) do { } while (0)
-#endif
+#include "common.cuh"
 
 namespace {
 
 constexpr int ROWS = 128;        // query rows per CTA = TMEM lanes
-constexpr int TK = 64;           // keys per tile
-constexpr int STAGES = 4;        // K/V stages, one per loader warp
+constexpr int TK = 128;          // keys per tile
+constexpr int KSTAGES = 3;       // K tiles in shared memory (the next tile's scores are taken a tile ahead)
+constexpr int VSTAGES = 2;       // V tiles
 constexpr int NUM_THREADS = 416; // warps 0-7 softmax, 8 MMA, 9-12 loaders
 constexpr uint32_t WAIT_LIMIT = 1u << 17;   // tries of about 100 ns each: some 13 ms, far beyond any legitimate wait
 
@@ -137,14 +133,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
 __device__ __forceinline__ float ex2(float x) {      // 2^x, one instruction; 2^-inf = 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -161,9 +149,9 @@ __device__ __forceinline__ uint32_t swz(int r, int c, int rows) {
 template <int HD>
 struct Smem {
   alignas(1024) uint8_t q[ROWS * HD * 2];
-  alignas(1024) uint8_t k[STAGES][TK * HD * 2];
-  alignas(1024) uint8_t v[STAGES][TK * HD * 2];
-  alignas(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], k_empty[STAGES], v_empty[STAGES], s_full[2], s_empty[2], p_full[2], pv_done[2];
+  alignas(1024) uint8_t k[KSTAGES][TK * HD * 2];
+  alignas(1024) uint8_t v[VSTAGES][TK * HD * 2];
+  alignas(8) uint64_t q_full, k_full[KSTAGES], v_full[VSTAGES], k_empty[KSTAGES], v_empty[VSTAGES], s_full[2], s_empty[2], p_full[2], pv_done[2];
   float xmax[2][2][ROWS];   // [tile parity][key half][row]: partial row maxima of the two threads of a row
   float xsum[2][ROWS];
   uint32_t tmem_base;
@@ -179,10 +167,10 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             int pages_cap, int* __restrict__ status) {
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int KSTEPS = HD / 16;          // MMA k-steps over the head dimension
-  constexpr uint32_t TMEM_COLS = 512;     // two S buffers of 64 columns, O of HD columns, two P buffers of 32 (a power of two is allocated)
-  constexpr uint32_t S_COL[2] = {0, 64};
-  constexpr uint32_t O_COL = 128;
-  constexpr uint32_t P_COL[2] = {256, 288};
+  constexpr uint32_t TMEM_COLS = 512;     // two S buffers of 128 columns, O of HD columns, two P buffers of 64
+  constexpr uint32_t S_COL[2] = {0, 128};
+  constexpr uint32_t O_COL = 256;
+  constexpr uint32_t P_COL[2] = {384, 448};
   // instruction descriptors: fp32 accumulate, bf16 operands; N at bit 17 (>> 3), M at bit 24 (>> 4); bit 16: B is MN-major
   constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
   constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
@@ -196,11 +184,6 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
   const int g = blockIdx.x % G;
   const int group = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef HK_TRACE
-  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 8 || warp == 9 || warp == 10);
-  int trace_i = 0;      // the probe count lives in a register: a probe is one clock read and two stores
-  if (threadIdx.x == 0 && blockIdx.x == 0) { hk_trace_n[0] = hk_trace_n[1] = hk_trace_n[2] = hk_trace_n[3] = 0; }
-#endif
   const int* bt = block_table + (size_t)it.slot * table_stride;
   const int t_begin = it.kv_lo / TK;
   const int t_end = (it.kv_hi + TK - 1) / TK;
@@ -212,10 +195,12 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 128);
-    for (int i = 0; i < STAGES; ++i) {
-      mbar_init(&sm.k_full[i], 32);
-      mbar_init(&sm.v_full[i], 32);
+    for (int i = 0; i < KSTAGES; ++i) {
+      mbar_init(&sm.k_full[i], 128);
       mbar_init(&sm.k_empty[i], 1);
+    }
+    for (int i = 0; i < VSTAGES; ++i) {
+      mbar_init(&sm.v_full[i], 128);
       mbar_init(&sm.v_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -262,17 +247,20 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
 
   if (warp >= 9) {
     // ================================================================= loaders (128 threads)
+    // The four warps copy every tile together: a thread copies chunk `c` of rows r0, r0 + RSTEP, ...; a row's
+    // page and offset are worked out once per tile (from the page ids preloaded into shared memory) and serve
+    // both K and V.  Copy groups go out in the order Q, K(0), V(0), K(1), V(1), ...; a thread tells the tensor
+    // core about a tile once its own copies of it have landed: after it has sent K(n) it waits for everything
+    // before that (so V(n - 1) is in), after V(n) likewise (so K(n) is in).  One tile's copies are always under
+    // way while the thread waits.
+    constexpr int RSTEP = 128 / CPR, NR = TK / RSTEP;
+    const int lt = threadIdx.x - 288;
+    const int c = lt % CPR, r0 = lt / CPR;
     bool q_signalled = false;
-    // Loader warp w owns stage w and tiles w, w + 4, ...: it can wait for its own copies to land without
-    // holding up the other three, so up to four tiles are on their way.  A lane copies chunk `c` of rows r0,
-    // r0 + RSTEP, ...; a row's page and offset are worked out once per tile (from the page ids preloaded into
-    // shared memory) and serve both K and V.
-    constexpr int RSTEP = 32 / CPR, NR = TK / RSTEP;
-    const int lw = warp - 9;
-    const int c = lane % CPR, r0 = lane / CPR;
-    for (int t = t_begin + lw; t < t_end; t += STAGES) {
-      const int n = t - t_begin, st = lw;
-      const uint32_t par = (uint32_t)((((n / STAGES) & 1)) ^ 1);      // a fresh barrier lets the first fill through
+    bool alive = true;
+    int n = 0;
+    for (int t = t_begin; t < t_end; ++t, ++n) {
+      const int ks_i = n % KSTAGES, vs_i = n % VSTAGES;
       size_t off[NR];
       uint32_t okbits = 0;
       // one division per tile; from there the page index and the place in the page advance by steps
@@ -290,37 +278,31 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
           ++pi;
         }
       }
-      TRACE(2 + (lw & 1));
-      if (!mbar_wait(&sm.k_empty[st], par, abort_flag)) break;
-      TRACE(2 + (lw & 1));
-      const uint32_t ks = smem_u32(sm.k[st]), vs = smem_u32(sm.v[st]);
+      if (!mbar_wait(&sm.k_empty[ks_i], (uint32_t)(((n / KSTAGES) & 1) ^ 1), abort_flag)) { alive = false; break; }   // a fresh barrier lets the first fill through
+      const uint32_t ks = smem_u32(sm.k[ks_i]), vs = smem_u32(sm.v[vs_i]);
 #pragma unroll
       for (int k = 0; k < NR; ++k) cp_async16(ks + swz(r0 + k * RSTEP, c, TK), k_pages + off[k], (okbits >> k) & 1u);
       cp_async_commit();
-      if (!mbar_wait(&sm.v_empty[st], par, abort_flag)) break;
-      TRACE(2 + (lw & 1));
+      cp_async_wait<1>();         // everything but K(n): Q and, from the second tile on, V(n - 1)
+      fence_async_proxy();
+      if (!q_signalled) {
+        mbar_arrive(&sm.q_full);
+        q_signalled = true;
+      } else {
+        mbar_arrive(&sm.v_full[(n - 1) % VSTAGES]);
+      }
+      if (!mbar_wait(&sm.v_empty[vs_i], (uint32_t)(((n / VSTAGES) & 1) ^ 1), abort_flag)) { alive = false; break; }
 #pragma unroll
       for (int k = 0; k < NR; ++k) cp_async16(vs + swz(r0 + k * RSTEP, c, TK), v_pages + off[k], (okbits >> k) & 1u);
       cp_async_commit();
-      if (!q_signalled) {         // Q went out first: it has landed when at most the two groups after it are pending
-        cp_async_wait<2>();
-        fence_async_proxy();
-        mbar_arrive(&sm.q_full);
-        q_signalled = true;
-      }
-      cp_async_wait<1>();
+      cp_async_wait<1>();         // everything but V(n): K(n) is in
       fence_async_proxy();
-      mbar_arrive(&sm.k_full[st]);
-      cp_async_wait<0>();
-      fence_async_proxy();
-      mbar_arrive(&sm.v_full[st]);
-      TRACE(2 + (lw & 1));
+      mbar_arrive(&sm.k_full[ks_i]);
     }
-    if (!q_signalled) {           // a loader warp without a tile of its own (short key ranges) still delivers its part of Q
-      cp_async_wait<0>();
-      fence_async_proxy();
-      mbar_arrive(&sm.q_full);
-    }
+    cp_async_wait<0>();
+    fence_async_proxy();
+    if (!q_signalled) mbar_arrive(&sm.q_full);        // no tile at all: Q alone
+    else if (alive && n > 0) mbar_arrive(&sm.v_full[(n - 1) % VSTAGES]);
   } else if (warp == 8) {
     // ================================================================= MMA issuer (one lane)
     if (lane == 0) {
@@ -328,16 +310,14 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       const uint32_t qs = smem_u32(sm.q);
       // scores of tile t into S buffer (t - t_begin) & 1
       auto issue_s = [&](int t) -> bool {
-        const int n = t - t_begin, st = n % STAGES, sb = n & 1;
-        TRACE(1);
-        if (!mbar_wait(&sm.k_full[st], (uint32_t)((n / STAGES) & 1), abort_flag)) return false;
-        TRACE(1);
+        const int n = t - t_begin, st = n % KSTAGES, sb = n & 1;
+        if (!mbar_wait(&sm.k_full[st], (uint32_t)((n / KSTAGES) & 1), abort_flag)) return false;
         if (!mbar_wait(&sm.s_empty[sb], (uint32_t)(((n >> 1) & 1) ^ 1), abort_flag)) return false;
         tc_fence_after();
         const uint32_t ks = smem_u32(sm.k[st]);
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
-          // half kk / 4 of the head (Q: 128 rows per half, K: 64), 32 bytes per step inside the swizzled row
+          // half kk / 4 of the head (Q and K: 128 rows per half), 32 bytes per step inside the swizzled row
           umma(tmem + S_COL[sb], desc_k_major(qs + (uint32_t)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32)),
                desc_k_major(ks + (uint32_t)((kk >> 2) * (TK * 128) + (kk & 3) * 32)), IDESC_S, kk ? 1u : 0u);
         }
@@ -347,13 +327,10 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       };
       if (ok && t_begin < t_end) ok = issue_s(t_begin);
       for (int t = t_begin; t < t_end && ok; ++t) {
-        const int n = t - t_begin, st = n % STAGES;
+        const int n = t - t_begin, st = n % VSTAGES;
         if (t + 1 < t_end && !issue_s(t + 1)) { ok = false; break; }    // next tile's scores run under this tile's softmax
-        TRACE(1);
         if (!mbar_wait(&sm.p_full[n & 1], (uint32_t)((n >> 1) & 1), abort_flag)) { ok = false; break; }
-        TRACE(1);
-        if (!mbar_wait(&sm.v_full[st], (uint32_t)((n / STAGES) & 1), abort_flag)) { ok = false; break; }
-        TRACE(1);
+        if (!mbar_wait(&sm.v_full[st], (uint32_t)((n / VSTAGES) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t vs = smem_u32(sm.v[st]);
 #pragma unroll
@@ -383,12 +360,11 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     bool ok = true;
     for (int t = t_begin; t < t_end; ++t) {
       const int n = t - t_begin, sb = n & 1;
-      TRACE(0);
       if (!__all_sync(0xffffffffu, mbar_wait(&sm.s_full[sb], (uint32_t)((n >> 1) & 1), abort_flag))) { ok = false; break; }
-      TRACE(0);
       tc_fence_after();
       uint32_t su[HK];
       tmem_ld32(lane_addr + S_COL[sb] + (uint32_t)(half * HK), su);
+      tmem_ld32(lane_addr + S_COL[sb] + (uint32_t)(half * HK + 32), su + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&sm.s_empty[sb]);                  // the S buffer may be overwritten by the tile after next
@@ -424,11 +400,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       // before the last one, which has to be complete.  O may only be touched once the product of the last tile has
       // finished, which matters only when the reference moves.  (Two barriers, alternating by tile: a parity wait
       // must never be two completions behind its barrier.)
-      TRACE(0);
       const bool any_move = __any_sync(0xffffffffu, n > 0 && move);
       const int need = any_move ? n - 1 : n - 2;     // the P V product that has to be complete by now
       if (need >= 0 && !__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[need & 1], (uint32_t)((need >> 1) & 1), abort_flag))) { ok = false; break; }
-      TRACE(0);
       tc_fence_after();
       uint32_t pw[HK / 2];
 #pragma unroll
@@ -439,8 +413,7 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         pw[e] = *reinterpret_cast<uint32_t*>(&pk);
       }
-      tmem_st16(lane_addr + P_COL[sb] + (uint32_t)(half * (HK / 2)), pw);
-      TRACE(0);
+      tmem_st32(lane_addr + P_COL[sb] + (uint32_t)(half * (HK / 2)), pw);
       // tensor-memory loads and stores are warp-wide: if any row of the warp moved its reference, the whole warp
       // goes through its half of the O columns (the others multiply by one)
       if (any_move) {
@@ -456,11 +429,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
       }
       tmem_st_wait();                                // P (and O) are in tensor memory before the tensor core is told
       m = mn;
-      TRACE(0);
-      TRACE(0);
       tc_fence_before();
       mbar_arrive(&sm.p_full[n & 1]);
-      TRACE(0);
     }
     sm.xsum[half][r] = l;
     asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
@@ -514,6 +484,367 @@ int launch(const void* q, const void* kp, const void* vp, const int* bt, int str
   return hk_launch_status();
 }
 
+
+// =================================================================================================================
+// Two query tiles per CTA.  256 rows = two tiles of 128 (token, head) rows share every K/V tile, and each tile has
+// softmax warps of its own (four: one thread per row, no exchange between threads), so that one tile's chain of
+// hand-offs (scores ready -> tensor-memory load -> exponentials -> tensor-memory store -> product) runs while the
+// other tile's products occupy the tensor pipe.  Tensor memory (512 columns): per tile 128 columns of scores, which
+// the probabilities overwrite in place (bf16, the first 64 columns), and HD columns of O.  Because P lies where S
+// lay, a tile's next scores are issued after its P V product; tensor-core instructions of one thread run in the
+// order they were issued, so they overwrite P only once that product has read it, and a commit after them says
+// that everything before is complete (which is why the softmax may touch O once it has seen the next scores).
+//
+//   warps 0-3 / 4-7   softmax of tile A / B: the row's 128 scores -> registers, mask, maximum, lazy rescaling of O,
+//                     exponentials, P -> tensor memory; at the end O / sum -> out
+//   warp 8 (1 lane)   issues S_A S_B | PV_A S_A' | PV_B S_B' | ...
+//   warp 9 (1 lane)   TMA: K and V tiles of 128 keys, page by page (a box of {64 columns, the page's keys, 1 half
+//                     of the head}), into two K and two V stages laid out [half][key][128 bytes], 128-byte swizzle
+//
+// Q is loaded by the softmax threads (each its own row, cp.async).  The cache pages must be TMA-able as whole
+// boxes: 128 % page_tokens == 0 with page_tokens a multiple of 8, or page_tokens a multiple of 128.
+constexpr int NT2 = 320;
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+template <int HD>
+struct Smem2 {
+  alignas(1024) uint8_t q[2][ROWS * HD * 2];
+  alignas(1024) uint8_t k[2][TK * HD * 2];
+  alignas(1024) uint8_t v[2][TK * HD * 2];
+  alignas(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full[2], o_done[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int pages[1];        // [pages_cap]
+};
+
+template <int HD>
+__global__ void __launch_bounds__(NT2, 1)
+attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                             const bf16* __restrict__ q, const int* __restrict__ block_table, int table_stride,
+                             const Item* __restrict__ items, bf16* __restrict__ out, int H, int G, int page_tokens, int window,
+                             float scale_log2, int pages_cap, int* __restrict__ status) {
+  constexpr int CPR = HD / 8;
+  constexpr int KSTEPS = HD / 16;
+  constexpr int HALVES = HD / 64;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t SP_COL[2] = {0, 128};
+  constexpr uint32_t O_COL[2] = {256, 256 + HD};
+  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  Smem2<HD>& sm = *reinterpret_cast<Smem2<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  volatile int* abort_flag = &sm.abort_flag;
+
+  const Item it = items[blockIdx.x / G];
+  const int g = blockIdx.x % G;
+  const int group = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* bt = block_table + (size_t)it.slot * table_stride;
+  const int t_begin = it.kv_lo / TK;
+  const int t_end = (it.kv_hi + TK - 1) / TK;
+  const int n_rows = it.n_tokens * group;
+  const bool two = n_rows > ROWS;                 // the second tile has rows at all
+  int* pages = sm.pages;
+  const int page_lo = it.kv_lo / page_tokens;
+  const int n_pages = it.kv_hi > it.kv_lo ? min((it.kv_hi - 1) / page_tokens - page_lo + 1, pages_cap) : 0;
+  for (int i = threadIdx.x; i < n_pages; i += NT2) pages[i] = bt[page_lo + i];
+  // K and V stages start as zeros: a box that is not copied (a page outside the key range that the request does
+  // not hold) leaves its rows as they are, and whatever is there is multiplied by a probability of zero
+  {
+    uint4* z = reinterpret_cast<uint4*>(sm.k[0]);
+    constexpr int N16 = 4 * TK * HD * 2 / 16;      // k[2] and v[2] are contiguous
+    for (int i = threadIdx.x; i < N16; i += NT2) z[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.q_full, 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.k_full[i], 1);
+      mbar_init(&sm.v_full[i], 1);
+      mbar_init(&sm.k_empty[i], 1);
+      mbar_init(&sm.v_empty[i], 1);
+      mbar_init(&sm.s_full[i], 1);
+      mbar_init(&sm.p_full[i], 128);
+      mbar_init(&sm.o_done[i], 1);
+    }
+    sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp < 8) {
+    // Q: every softmax thread sends for its own row (token r / group, head r % group); rows past the item are zero
+    const int qt = warp >> 2, r = threadIdx.x & 127, row = qt * ROWS + r;
+    const bool ok = row < n_rows;
+    const int tok = ok ? row / group : 0, head = ok ? row - tok * group : 0;
+    const bf16* src = q + ((size_t)(it.q_row0 + tok) * H + g * group + head) * HD;
+    const uint32_t qs = smem_u32(sm.q[qt]);
+#pragma unroll
+    for (int c = 0; c < CPR; ++c) cp_async16(qs + swz(r, c, ROWS), src + c * 8, ok);
+    cp_async_commit();
+  }
+  fence_async_proxy();            // the zeros above, before the TMA writes of the async proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const int n_tiles = t_end - t_begin;
+
+  if (warp == 9) {
+    // ================================================================= TMA producer (one warp; a lane per box)
+    // With small pages a tile is many boxes (16-token pages: 8 boxes of 2 KB per half for K and as many for V), so
+    // the lanes issue them side by side; lane 0 alone waits for the stage and announces the bytes.
+    const int box_rows = page_tokens < TK ? page_tokens : TK;
+    const int boxes = TK / box_rows;                                   // at most 16
+    const uint32_t box_bytes = (uint32_t)box_rows * 128u;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int t = t_begin + n, st = n & 1;
+      const uint32_t par = (uint32_t)(((n >> 1) & 1) ^ 1);            // a fresh barrier lets the first fill through
+      // this lane's box of the tile: does it hold keys of the range, and does the request hold its page?
+      int row = -1;
+      if (lane < boxes) {
+        const int j = t * TK + lane * box_rows;
+        const int pi = j / page_tokens - page_lo;
+        if (j < it.kv_hi && j + box_rows > it.kv_lo && pi >= 0 && pi < n_pages && pages[pi] >= 0)
+          row = (pages[pi] * G + g) * page_tokens + (j % page_tokens);
+      }
+      const uint32_t bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, row >= 0)) * box_bytes * HALVES;
+      bool alive = true;
+      for (int kv = 0; kv < 2 && alive; ++kv) {
+        uint64_t* full = kv == 0 ? &sm.k_full[st] : &sm.v_full[st];
+        int go = 1;
+        if (lane == 0) {
+          go = mbar_wait(kv == 0 ? &sm.k_empty[st] : &sm.v_empty[st], par, abort_flag) ? 1 : 0;
+          if (go) {
+            if (bytes == 0) mbar_arrive(full);
+            else mbar_expect_tx(full, bytes);
+          }
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { alive = false; break; }
+        if (row >= 0) {
+          const uint32_t base = smem_u32(kv == 0 ? sm.k[st] : sm.v[st]) + (uint32_t)(lane * box_rows) * 128u;
+          const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) tma_load_3d(base + (uint32_t)h * (TK * 128), map, full, 0, row, h);
+        }
+      }
+      if (!alive) break;
+    }
+  } else if (warp == 8) {
+    // ================================================================= MMA issuer (one lane)
+    if (lane == 0) {
+      bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
+      const int nq = two ? 2 : 1;
+      auto issue_s = [&](int qt, int n) {
+        const uint32_t qs = smem_u32(sm.q[qt]), ks = smem_u32(sm.k[n & 1]);
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk)
+          umma(tmem + SP_COL[qt], desc_k_major(qs + (uint32_t)((kk >> 2) * (ROWS * 128) + (kk & 3) * 32)),
+               desc_k_major(ks + (uint32_t)((kk >> 2) * (TK * 128) + (kk & 3) * 32)), IDESC_S, kk ? 1u : 0u);
+        umma_commit(&sm.s_full[qt]);
+      };
+      if (ok && n_tiles > 0) {
+        ok = mbar_wait(&sm.k_full[0], 0, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          for (int qt = 0; qt < nq; ++qt) issue_s(qt, 0);
+          umma_commit(&sm.k_empty[0]);
+        }
+      }
+      for (int n = 0; n < n_tiles && ok; ++n) {
+        const int st = n & 1;
+        const uint32_t vs = smem_u32(sm.v[st]);
+        for (int qt = 0; qt < nq && ok; ++qt) {
+          if (!mbar_wait(&sm.p_full[qt], (uint32_t)(n & 1), abort_flag)) { ok = false; break; }
+          if (qt == 0 && !mbar_wait(&sm.v_full[st], (uint32_t)((n >> 1) & 1), abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < TK / 16; ++kk)
+            umma_ts(tmem + O_COL[qt], tmem + SP_COL[qt] + (uint32_t)(kk * 8), desc_mn_major(vs + (uint32_t)kk * 2048u, (uint32_t)(TK * 128)),
+                    IDESC_O, (n > 0 || kk > 0) ? 1u : 0u);
+          if (qt == nq - 1) umma_commit(&sm.v_empty[st]);
+          if (n + 1 < n_tiles) {
+            if (qt == 0 && !mbar_wait(&sm.k_full[(n + 1) & 1], (uint32_t)(((n + 1) >> 1) & 1), abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(qt, n + 1);       // after this tile's P V: it overwrites the P that product reads
+            if (qt == nq - 1) umma_commit(&sm.k_empty[(n + 1) & 1]);
+          } else {
+            umma_commit(&sm.o_done[qt]);
+          }
+        }
+      }
+    }
+  } else {
+    // ================================================================= softmax (two groups of 128 threads, one per row)
+    const int qt = warp >> 2, quarter = warp & 3;
+    const int r = quarter * 32 + lane;                 // row of the tile = TMEM lane
+    const int row = qt * ROWS + r;
+    const int tq = row / group;
+    const bool valid = row < n_rows;
+    const int pos = it.pos0 + (valid ? tq : 0);
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    cp_async_wait<0>();
+    fence_async_proxy();
+    mbar_arrive(&sm.q_full);
+    float m = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+    bool ok = true;
+    if (qt == 0 || two) {
+      for (int n = 0; n < n_tiles; ++n) {
+        const int t = t_begin + n;
+        if (!__all_sync(0xffffffffu, mbar_wait(&sm.s_full[qt], (uint32_t)(n & 1), abort_flag))) { ok = false; break; }
+        tc_fence_after();
+        uint32_t su[TK];
+#pragma unroll
+        for (int c0 = 0; c0 < TK; c0 += 32) tmem_ld32(lane_addr + SP_COL[qt] + (uint32_t)c0, su + c0);
+        tmem_ld_wait();
+        const int j0 = t * TK;
+        const bool whole = valid && j0 >= max(lo, it.kv_lo) && j0 + TK - 1 <= min(pos, it.kv_hi - 1);
+        if (!whole) {
+#pragma unroll
+          for (int i = 0; i < TK; ++i) {
+            const int j = j0 + i;
+            const bool see = valid && j >= lo && j <= pos && j >= it.kv_lo && j < it.kv_hi;
+            if (!see) su[i] = 0xff800000u;             // -inf
+          }
+        }
+        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int i = 0; i < TK; i += 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(su[i + e]));
+        }
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+        // Lazy rescaling, as in the one-tile kernel: the reference maximum moves only when the row's maximum has run
+        // ahead of it by more than 2^8.  The scores of this tile are complete, and so is every product issued before
+        // them, the last P V among them: O may be touched.
+        const bool move = mt > m + 8.0f;
+        const float mn = move ? mt : m;
+        const float msafe = mn == -CUDART_INF_F ? 0.f : mn;
+        const float corr = move ? exp2f(m - msafe) : 1.0f;
+        l0 *= corr;
+        l1 *= corr;
+        if (__any_sync(0xffffffffu, n > 0 && move)) {
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
+          }
+        }
+        m = mn;
+#pragma unroll
+        for (int c0 = 0; c0 < TK; c0 += 64) {
+          uint32_t pw[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float p0 = ex2(fmaf(__uint_as_float(su[c0 + 2 * e]), scale_log2, -msafe));
+            const float p1 = ex2(fmaf(__uint_as_float(su[c0 + 2 * e + 1]), scale_log2, -msafe));
+            l0 += p0;
+            l1 += p1;
+            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+            pw[e] = *reinterpret_cast<uint32_t*>(&pk);
+          }
+          tmem_st32(lane_addr + SP_COL[qt] + (uint32_t)(c0 / 2), pw);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full[qt]);
+      }
+      if (ok && n_tiles > 0 && __all_sync(0xffffffffu, mbar_wait(&sm.o_done[qt], 0, abort_flag))) {
+        tc_fence_after();
+        const float l = l0 + l1;
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        bf16* op = out + ((size_t)(it.q_row0 + (valid ? tq : 0)) * H + g * group + (valid ? row % group : 0)) * HD;
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
+                w[e] = *reinterpret_cast<uint32_t*>(&pk);
+              }
+              *reinterpret_cast<uint4*>(op + c0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && sm.abort_flag) atomicExch(status, 3);
+  if (warp == 8) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// The cache pages of one layer, a bf16 matrix [rows, hd], seen as [64 columns, rows, hd / 64 halves]; a box takes
+// 64 columns x box_rows rows of one half and lands as [row][128 bytes] with the 128-byte swizzle.  The map covers
+// this GPU's own memory; the loads use no multicast.
+bool make_page_map(CUtensorMap* map, const void* ptr, unsigned long long rows, int hd, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(hd / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)hd * 2, 128u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+int launch2(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const int* bt, int stride, const void* items, int n_items,
+            void* out, int H, int G, int pt, int window, float scale_log2, int pages_cap, int* status, cudaStream_t s) {
+  const size_t smem = sizeof(Smem2<HD>) + 1024 + (size_t)pages_cap * sizeof(int);
+  if (smem > 225 * 1024) return HK_ERR_UNSUPPORTED;
+  static HkSmemCache allowed = {};
+  if (int e = hk_allow_smem(attention_prefill_tc2_kernel<HD>, smem, allowed)) return e;
+  dim3 grid((unsigned)n_items * (unsigned)G);
+  return hk_launch(attention_prefill_tc2_kernel<HD>, grid, dim3(NT2), smem, s, mk, mv, (const bf16*)q, bt, stride, (const Item*)items,
+                   (bf16*)out, H, G, pt, window, scale_log2, pages_cap, status);
+}
+
 }  // namespace
 
 // items: n_items records of 8 ints {first query row, query tokens (at most 128 / (H / G)), request slot, position
@@ -532,11 +863,24 @@ HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const voi
   return HK_ERR_UNSUPPORTED;
 }
 
-#ifdef HK_TRACE
-// Copies the probes of the last traced launch to the host: out[4][512] clocks, counts[4].
-HK_API int hk_attention_prefill_tc_trace(long long* out, int* counts) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, hk_trace_buf, sizeof(long long) * 4 * 512);
-  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(counts, hk_trace_n, sizeof(int) * 4);
-  return (int)e;
+// The same for items of up to 256 / (H / G) query tokens (two query tiles per CTA, K and V by TMA).  `num_pages`:
+// pages of the cache tensors.  Refuses (HK_ERR_UNSUPPORTED) what hk_attention_prefill_tc refuses and page sizes
+// whose pages are not whole TMA boxes of a 128-key tile: it takes multiples of 8 that divide 128, and multiples of 128.
+HK_API int hk_attention_prefill_tc2(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
+                                    const int* block_table, int table_stride, const void* items, int n_items, void* out, int H,
+                                    int G, int hd, int page_tokens, int window, float scale_log2, int pages_cap, int* status,
+                                    void* stream) {
+  if (n_items <= 0) return 0;
+  if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
+  if (hd != 64 && hd != 128) return HK_ERR_UNSUPPORTED;
+  const bool boxes_ok = (page_tokens % 8 == 0 && TK % page_tokens == 0) || page_tokens % TK == 0;
+  if (!boxes_ok) return HK_ERR_UNSUPPORTED;
+  if ((((uintptr_t)q | (uintptr_t)out) & 15) != 0 || (((uintptr_t)k_pages | (uintptr_t)v_pages) & 127) != 0) return HK_ERR_UNSUPPORTED;
+  const int box_rows = page_tokens < TK ? page_tokens : TK;
+  const unsigned long long rows = (unsigned long long)num_pages * G * page_tokens;
+  CUtensorMap mk, mv;
+  if (!make_page_map(&mk, k_pages, rows, hd, box_rows) || !make_page_map(&mv, v_pages, rows, hd, box_rows)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 128) return launch2<128>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
+  return launch2<64>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
 }
-#endif

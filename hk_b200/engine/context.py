@@ -24,7 +24,7 @@ class StepContext:
     q_lens (rows), start_positions (position of the first row).
     `tables[key]` = (device views of the arrays by name, info) for every part that named tables with `key`.
     `fixed_shape`: this step is (or will be replayed as) a captured graph: table shapes and `info` may depend
-    only on the number of rows and on `max_context`.
+    only on the number of rows and on `max_context`.  `page_tokens`: the cache's page size.
     """
     precision: Precision
     n_tokens: int
@@ -38,6 +38,7 @@ class StepContext:
     tables: Dict[Hashable, Tuple[Dict[str, torch.Tensor], object]] = field(default_factory=dict)
     fixed_shape: bool = False
     max_context: int = 0
+    page_tokens: int = 0        # tokens per cache page (0: not said); a part may cut its work to fit the pages
 
 
 def table_parts(model: Part) -> List[Tuple[Hashable, Part]]:

@@ -351,7 +351,7 @@ class Engine:
             self.steps_run += 1
             return g.run(meta, slots, starts, on_device, n)
         ctx = StepContext(self.precision, n, None, None, None, slots, q_starts, q_lens, starts,
-                          max_context=self.max_context)
+                          max_context=self.max_context, page_tokens=self.cache.page_tokens)
         packed = pack_step(meta, ctx, self._table_parts)
         bind_step(ctx, packed, self.stager.upload(packed.host))
         fill_device_tokens(ctx.token_ids, on_device)

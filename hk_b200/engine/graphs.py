@@ -46,7 +46,7 @@ class DecodeGraph:
         eng = self.engine
         b = self.batch
         return StepContext(eng.precision, b, None, None, None, list(slots), list(range(b)), [1] * b, list(starts),
-                           fixed_shape=True, max_context=eng.max_context)
+                           fixed_shape=True, max_context=eng.max_context, page_tokens=eng.cache.page_tokens)
 
     def run(self, meta: np.ndarray, slots, starts, on_device=(), n_real: int = 0) -> torch.Tensor:
         """meta: int32 [3, B] (token ids, positions, slots); `on_device`: (row, DeviceToken) pairs whose ids are

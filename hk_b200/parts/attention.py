@@ -107,11 +107,15 @@ class GQAAttention(Part):
         from ..csrc import attention_fast
         H, G, hd = self.H, self.G, self.hd
         tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp"
+        rows = 128 if tc else 64
+        # portions of more than 128 rows take the kernel with two query tiles per CTA, where the pages allow it
+        if tc and max(ctx.q_lens) * (H // G) > 128 and attention_fast.tc2_prefill_supported(hd, H // G, ctx.page_tokens):
+            rows = 256
         fixed = attention_fast.decode_splits(ctx.n_tokens, G, self._sm_count) if ctx.fixed_shape else 0
         got = attention_fast.plan_arrays(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens,
                                          self.window or 0, H, G, self._sm_count, fixed_splits=fixed,
                                          max_context=ctx.max_context if ctx.fixed_shape else 0,
-                                         prefill_rows=128 if tc else 64)
+                                         prefill_rows=rows)
         if got is None:
             return None
         items, merge, info = got

@@ -99,6 +99,7 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--cluster", type=int, default=0, help="gemm_smallm: pin the CTAs per cluster that split K (1, 2 or 4)")
     ap.add_argument("--mma", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
+    ap.add_argument("--one-tile", action="store_true", help="attn_prefill: the tcgen05 kernel with one query tile per CTA")
     ap.add_argument("--row-warps", type=int, default=0, help="gemm_stream: consumer warps across a tile's rows (8, 4, 2 or 1)")
     ap.add_argument("--ctas", type=int, default=0, help="gemm_stream: run this many CTAs instead of one per SM")
     ap.add_argument("--row-tiles", type=int, default=0, help="gemm_smallm: pin the row tiles of 16 per CTA (1, 2 or 4)")
@@ -153,8 +154,10 @@ def main(argv=None) -> int:
             q = torch.randn(n, H * hd, device=dev).to(torch.bfloat16)
             pos = torch.arange(n, dtype=torch.int32, device=dev)
             slot = torch.zeros(n, dtype=torch.int32, device=dev)
-            plan = attention_fast.build_plan([0], [0], [n], [0], n, 0, H, G, sms, upload,
-                                             prefill_rows=128 if attention_fast.tc_prefill_supported(hd, H // G) and not a.mma else 64)
+            rows = 64
+            if attention_fast.tc_prefill_supported(hd, H // G) and not a.mma:
+                rows = 256 if attention_fast.tc2_prefill_supported(hd, H // G, pt) and not a.one_tile else 128
+            plan = attention_fast.build_plan([0], [0], [n], [0], n, 0, H, G, sms, upload, prefill_rows=rows)
             nbytes = 2.0 * 2 * n * G * hd + 2 * 2.0 * n * H * hd
             flops = 4.0 * H * hd * n * (n + 1) / 2
         out = torch.empty_like(q)

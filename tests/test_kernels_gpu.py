@@ -258,7 +258,7 @@ ATT_SHAPES = [(4, 2, 16, 4), (5, 1, 48, 16), (6, 2, 80, 8), (8, 2, 128, 16), (3,
               (2, 1, 112, 16), (3, 1, 40, 8), (4, 2, 160, 16), (2, 2, 24, 4)]
 
 
-def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=None, sm_count=148, fixed_splits=0):
+def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=None, sm_count=148, fixed_splits=0, rows=0):
     """q_spans: per slot (first position, count) of the query rows; the cache holds lens[s] keys."""
     rng = np.random.default_rng(H * 1000 + hd + pt + window)
     k_pages, v_pages, bt, dk, dv = make_paged(rng, len(lens), lens, G, hd, pt, dtype)
@@ -291,7 +291,7 @@ def attention_case(kernel, dtype, H, G, hd, pt, window, lens, q_spans, spike=Non
         plan = attention_fast.build_plan(list(range(len(lens))), q_starts, [c for _, c in q_spans], [p0 for p0, _ in q_spans],
                                          n, window, H, G, sm_count, lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV),
                                          fixed_splits=fixed_splits,
-                                         prefill_rows=128 if kernel == "flash" and attention_fast.tc_prefill_supported(hd, H // G) else 64)
+                                         prefill_rows=rows or (128 if kernel == "flash" and attention_fast.tc_prefill_supported(hd, H // G) else 64))
     with ops().force(attention=kernel):
         ops().paged_attention(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), bt.to(DEV), pos_t.to(DEV), slot_t.to(DEV), out,
                               H, G, hd, pt, window, scale, plan=plan)
@@ -546,6 +546,34 @@ def test_attention_tcgen05_prefill_long_prompt(H, G, hd, pt, window):
     close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
     from hk_b200.csrc import gemm_fast
     gemm_fast.check_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("H,G,hd,pt,window", [(32, 8, 128, 16, 0), (8, 2, 64, 16, 0), (6, 2, 128, 32, 200), (5, 1, 64, 16, 0), (16, 1, 128, 8, 0),
+                                              (3, 3, 128, 64, 0), (4, 1, 64, 128, 150), (8, 2, 128, 256, 0), (12, 4, 64, 16, 131)])
+def test_attention_tcgen05_two_query_tiles(H, G, hd, pt, window):
+    # items of 256 rows (two query tiles per CTA, K and V by TMA, P written over S): a 700-token prompt whole, a portion
+    # that starts at position 391 of another request, a portion of 40 tokens (rows in the first tile only for some
+    # groupings) and a single token at position 299
+    out, want, _ = attention_case("flash", torch.bfloat16, H, G, hd, pt, window, [700, 650, 77, 300],
+                                  [(0, 700), (391, 259), (37, 40), (299, 1)], rows=256)
+    close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+    from hk_b200.csrc import gemm_fast
+    gemm_fast.check_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("j", [0, 15, 127, 128, 129, 255, 256, 383, 384, 600, 699])
+def test_attention_tcgen05_two_query_tiles_find_a_far_key(j):
+    # row 699 of a 700-token prompt (the last row of some CTA's second tile) with one dominant key at a tile's or a
+    # page's edge; and the first row of a second tile (row 32 * 5 + 128 / 4 ...) likewise
+    H, G, hd, pt = 8, 2, 128, 16
+    for row in (699, 32 * 21):
+        if j > row:
+            continue
+        out, want, (q, dk, dv, slot, pos) = attention_case("flash", torch.bfloat16, H, G, hd, pt, 0, [700], [(0, 700)],
+                                                           spike=(row, 0, j, 1), rows=256)
+        close(out, want, torch.bfloat16, atol=3e-3, rtol=2 ** -7)
+        got = out.double().cpu().reshape(700, H, hd)
+        assert torch.allclose(got[row, 4], dv[0][j, 1], atol=0.05) and not torch.allclose(got[row, 0], dv[0][j, 1], atol=0.05)
 
 
 @pytest.mark.parametrize("kernel", ["flash", "flash_cp"])
