@@ -120,7 +120,7 @@ def build_dir() -> str:
 
 
 def _extra_flags() -> List[str]:
-    """Extra nvcc flags from HK_B200_NVCC_FLAGS (for instance -DHK_TRACE); they are part of a built file's name."""
+    """Extra nvcc flags from HK_B200_NVCC_FLAGS (for instance -Xptxas -v); they are part of a built file's name."""
     return os.environ.get("HK_B200_NVCC_FLAGS", "").split()
 
 

@@ -27,8 +27,6 @@ template <typename T, int PER>
 __global__ void embedding_vec_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                      int d, int vocab) {
   constexpr int E = 16 / sizeof(T);   // elements per 16-byte load
-  pdl_launch_dependents();
-  pdl_wait();
   int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -124,13 +122,11 @@ rms_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, co
   const float4* wv = reinterpret_cast<const float4*>(w);
   const int chunks = d >> 2;
   float4 v[PER], g[PER];
-  pdl_launch_dependents();
 #pragma unroll
   for (int k = 0; k < PER; ++k) {     // the norm's weight does not depend on the kernel before
     const int c = threadIdx.x + k * 256;
     if (c < chunks) g[k] = wv[c];
   }
-  pdl_wait();
   const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
@@ -226,8 +222,6 @@ __global__ void qk_norm_rope_kv_write_kernel(
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
     int write_kv, const float* __restrict__ bias, int pairing) {
   __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
-  pdl_launch_dependents();
-  pdl_wait();
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int heads_total = H + (write_kv ? 2 * G : 0);
   long long item = (long long)blockIdx.x * QKR_WARPS + wid;
@@ -294,8 +288,6 @@ qk_norm_rope_kv_write_vec_kernel(
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
     int write_kv, const float* __restrict__ bias, int pairing) {
-  pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int heads_total = H + (write_kv ? 2 * G : 0);
   const long long item = (long long)blockIdx.x * QKV_WARPS + wid;
@@ -427,8 +419,6 @@ HK_API int hk_add_bias(float* out, const float* bias, int n, int N, void* stream
 // `block` gates followed by the matching `block` ups (block == F: all gates, then all ups).
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block) {
-  pdl_launch_dependents();
-  pdl_wait();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   long long t = i / F;

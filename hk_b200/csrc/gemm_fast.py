@@ -69,16 +69,6 @@ def row_tiles(M: int, N: int, device) -> int:
     return _rt_override or 1
 
 
-_cs_override = 0
-
-
-def cluster_size(M: int, N: int, rt: int, device) -> int:
-    """CTAs per cluster that split K for one tile of 16 rows in the small-M kernel.  One: splitting K over a
-    cluster (partial sums through distributed shared memory) measured slower at every decode shape of the 8B
-    model, narrow outputs included - the cluster launch and its barrier cost more than the idle SMs."""
-    return _cs_override or 1
-
-
 _tc_bn = 0            # tests and tuning runs may pin the tile width (128 or 256) ...
 _tc_splits = 0        # ... and the number of K slices of the tcgen05 kernel
 
@@ -196,9 +186,8 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
         if M > SMALL_M:
             return False
         lib = build.load("gemm_smallm")
-        rt = row_tiles(M, N, a.device)
         code = lib.hk_gemm_smallm(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(N), 1 if accumulate else 0,
-                                  rt, cluster_size(M, N, rt, a.device), _stream())
+                                  row_tiles(M, N, a.device), _stream())
         if code == _UNSUPPORTED:
             return False
         ops._check(code, "gemm (small-M)")

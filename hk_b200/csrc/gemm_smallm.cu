@@ -12,11 +12,7 @@
 // skipped on store.  Needs K % 8 == 0 and 16-byte aligned a and w.
 //
 // Reference counterpart: `gemv_bf16` (warp per row, 16-byte loads, one token), src/cuda_device.zig:1294-1351.
-#include <cooperative_groups.h>
-
 #include "common.cuh"
-
-namespace cg = cooperative_groups;
 
 namespace {
 
@@ -36,18 +32,15 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
-// MT: token tiles of 8 (M <= 8*MT).  RT: row tiles of 16 per CTA.  CS: CTAs of a thread-block cluster that share
-// one tile of rows and split K among themselves (narrow outputs would otherwise leave SMs without work); their
-// partial sums meet in the first CTA's shared memory (distributed shared memory) and are added in rank order.
-template <int MT, int RT, bool ADD, int CS>
+// MT: token tiles of 8 (M <= 8*MT).  RT: row tiles of 16 per CTA.
+template <int MT, int RT, bool ADD>
 __global__ void __launch_bounds__(SM_WARPS * 32)
 gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ out, int M, int N, int K,
                    long long ldo) {
-  extern __shared__ float red[];   // [SM_WARPS][RT*16][MT*8], then (first CTA of a cluster) [CS - 1][RT*16][MT*8]
+  extern __shared__ float red[];   // [SM_WARPS][RT*16][MT*8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int crank = CS > 1 ? (int)(blockIdx.x % CS) : 0;     // rank in the cluster (clusters are consecutive blocks)
-  const int n0 = (int)(blockIdx.x / CS) * (RT * 16);
+  const int n0 = (int)blockIdx.x * (RT * 16);
 
   float acc[RT][MT][4];
 #pragma unroll
@@ -57,11 +50,10 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[r][j][e] = 0.f;
 
-  // this warp's share of the 64-wide chunks of K (the cluster's CTAs, then the CTA's warps, cut K evenly)
+  // this warp's share of the 64-wide chunks of K (the CTA's warps cut K evenly)
   const int chunks = (K + KCHUNK - 1) / KCHUNK;
-  const int part = crank * SM_WARPS + warp;
-  const int c_begin = (int)((long long)chunks * part / (SM_WARPS * CS));
-  const int c_end = (int)((long long)chunks * (part + 1) / (SM_WARPS * CS));
+  const int c_begin = (int)((long long)chunks * warp / SM_WARPS);
+  const int c_end = (int)((long long)chunks * (warp + 1) / SM_WARPS);
 
   const bf16* wrow[RT][2];
 #pragma unroll
@@ -111,7 +103,6 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
   // waits for that kernel's output (the activations).
   if (c_begin < c_end) load_w(c_begin, 0);
   if (c_begin + 1 < c_end) load_w(c_begin + 1, 1);
-  pdl_wait();
   for (int c = c_begin; c < c_end; c += 2) {
     uint4 cur[RT][2][2];
 #pragma unroll
@@ -148,98 +139,46 @@ gemm_smallm_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float
       mine[(r * 16 + g + 8) * COLS + col + 1] = acc[r][j][3];
     }
   __syncthreads();
-  if (CS == 1) {
-    for (int i = threadIdx.x; i < ROWS * COLS; i += SM_WARPS * 32) {
-      const int row = i % ROWS, m = i / ROWS;    // rows fastest: consecutive threads write consecutive floats
-      if (m >= M || n0 + row >= N) continue;
-      float s = 0.f;
+  for (int i = threadIdx.x; i < ROWS * COLS; i += SM_WARPS * 32) {
+    const int row = i % ROWS, m = i / ROWS;    // rows fastest: consecutive threads write consecutive floats
+    if (m >= M || n0 + row >= N) continue;
+    float s = 0.f;
 #pragma unroll
-      for (int wv = 0; wv < SM_WARPS; ++wv) s += red[(size_t)wv * ROWS * COLS + row * COLS + m];
-      float* o = out + (size_t)m * ldo + n0 + row;
-      *o = ADD ? *o + s : s;
-    }
-  } else {
-    cg::cluster_group cluster = cg::this_cluster();
-    float* inbox = red + (size_t)SM_WARPS * ROWS * COLS;        // [CS - 1][ROWS * COLS] in the first CTA
-    if (crank != 0) {
-      float* remote = cluster.map_shared_rank(inbox, 0) + (size_t)(crank - 1) * ROWS * COLS;
-      for (int i = threadIdx.x; i < ROWS * COLS; i += SM_WARPS * 32) {
-        const int row = i % ROWS, m = i / ROWS;
-        float s = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < SM_WARPS; ++wv) s += red[(size_t)wv * ROWS * COLS + row * COLS + m];
-        remote[i] = s;
-      }
-    }
-    cluster.sync();          // the partial sums of the other CTAs are in the first CTA's inbox
-    if (crank == 0) {
-      for (int i = threadIdx.x; i < ROWS * COLS; i += SM_WARPS * 32) {
-        const int row = i % ROWS, m = i / ROWS;
-        if (m >= M || n0 + row >= N) continue;
-        float s = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < SM_WARPS; ++wv) s += red[(size_t)wv * ROWS * COLS + row * COLS + m];
-#pragma unroll
-        for (int r = 1; r < CS; ++r) s += inbox[(size_t)(r - 1) * ROWS * COLS + i];
-        float* o = out + (size_t)m * ldo + n0 + row;
-        *o = ADD ? *o + s : s;
-      }
-    }
+    for (int wv = 0; wv < SM_WARPS; ++wv) s += red[(size_t)wv * ROWS * COLS + row * COLS + m];
+    float* o = out + (size_t)m * ldo + n0 + row;
+    *o = ADD ? *o + s : s;
   }
 }
 
-template <typename... KArgs, typename... Args>
-int launch_cluster(void (*kernel)(KArgs...), unsigned grid, int cs, size_t smem, cudaStream_t s, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(SM_WARPS * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cs;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-
-template <int MT, int RT, int CS>
+template <int MT, int RT>
 int launch(const void* a, const void* w, float* out, int M, int N, int K, long long ldo, int add, cudaStream_t s) {
-  const size_t smem = (size_t)(SM_WARPS + CS - 1) * RT * 16 * MT * 8 * sizeof(float);
+  const size_t smem = (size_t)SM_WARPS * RT * 16 * MT * 8 * sizeof(float);
   static HkSmemCache allowed_store = {}, allowed_add = {};
-  if (int e = hk_allow_smem(gemm_smallm_kernel<MT, RT, false, CS>, smem, allowed_store)) return e;
-  if (int e = hk_allow_smem(gemm_smallm_kernel<MT, RT, true, CS>, smem, allowed_add)) return e;
-  const unsigned grid = (unsigned)((N + RT * 16 - 1) / (RT * 16)) * CS;
-  if (CS > 1) {
-    if (add)
-      return launch_cluster(gemm_smallm_kernel<MT, RT, true, CS>, grid, CS, smem, s, (const bf16*)a, (const bf16*)w, out, M, N, K, ldo);
-    return launch_cluster(gemm_smallm_kernel<MT, RT, false, CS>, grid, CS, smem, s, (const bf16*)a, (const bf16*)w, out, M, N, K, ldo);
-  }
+  if (int e = hk_allow_smem(gemm_smallm_kernel<MT, RT, false>, smem, allowed_store)) return e;
+  if (int e = hk_allow_smem(gemm_smallm_kernel<MT, RT, true>, smem, allowed_add)) return e;
+  const unsigned grid = (unsigned)((N + RT * 16 - 1) / (RT * 16));
   if (add)
-    return hk_launch_pdl(gemm_smallm_kernel<MT, RT, true, 1>, dim3(grid), dim3(SM_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w,
-                         out, M, N, K, ldo);
-  return hk_launch_pdl(gemm_smallm_kernel<MT, RT, false, 1>, dim3(grid), dim3(SM_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w,
-                       out, M, N, K, ldo);
+    return hk_launch(gemm_smallm_kernel<MT, RT, true>, dim3(grid), dim3(SM_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w, out,
+                     M, N, K, ldo);
+  return hk_launch(gemm_smallm_kernel<MT, RT, false>, dim3(grid), dim3(SM_WARPS * 32), smem, s, (const bf16*)a, (const bf16*)w, out, M,
+                   N, K, ldo);
 }
 
 }  // namespace
 
-// rt: row tiles of 16 per CTA (1, 2 or 4).  cs: CTAs per cluster that split K for one tile of rows (1, 2 or 4; above
-// 1 only with rt = 1).  Refuses (HK_ERR_UNSUPPORTED) M > 64, K % 8 != 0, unaligned operands.
+// rt: row tiles of 16 per CTA (1, 2 or 4).  Refuses (HK_ERR_UNSUPPORTED) M > 64, K % 8 != 0, unaligned operands.
 HK_API int hk_gemm_smallm(const void* a, const void* w, float* out, int M, int N, int K, long long ldo, int add, int rt,
-                          int cs, void* stream) {
+                          void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   const int mt = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-#define HK_CASE(MT, RT, CS) \
-  if (mt == MT && rt == RT && cs == CS) return launch<MT, RT, CS>(a, w, out, M, N, K, ldo, add, s);
-  HK_CASE(1, 1, 1) HK_CASE(1, 2, 1) HK_CASE(1, 4, 1) HK_CASE(1, 1, 2) HK_CASE(1, 1, 4)
-  HK_CASE(2, 1, 1) HK_CASE(2, 2, 1) HK_CASE(2, 4, 1) HK_CASE(2, 1, 2) HK_CASE(2, 1, 4)
-  HK_CASE(4, 1, 1) HK_CASE(4, 2, 1)
-  HK_CASE(8, 1, 1) HK_CASE(8, 2, 1)
+#define HK_CASE(MT, RT) \
+  if (mt == MT && rt == RT) return launch<MT, RT>(a, w, out, M, N, K, ldo, add, s);
+  HK_CASE(1, 1) HK_CASE(1, 2) HK_CASE(1, 4)
+  HK_CASE(2, 1) HK_CASE(2, 2) HK_CASE(2, 4)
+  HK_CASE(4, 1) HK_CASE(4, 2)
+  HK_CASE(8, 1) HK_CASE(8, 2)
 #undef HK_CASE
   return HK_ERR_UNSUPPORTED;
 }

@@ -36,14 +36,6 @@
 
 #include "common.cuh"
 
-#ifdef HK_TRACE
-// Timing probes (built with -DHK_TRACE only): probe p of CTA b holds the global timer in nanoseconds.
-__device__ unsigned long long hk_stream_trace[160][8];
-#define TRACE(p) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); hk_stream_trace[blockIdx.x % 160][p] = t_; } while (0)
-#else
-#define TRACE(p) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int CONSUMERS = 8;
@@ -172,7 +164,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int own_first = shared_tiles + (int)blockIdx.x * own;
 
   if (threadIdx.x == 0) {
-    TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], CONSUMERS);
@@ -198,9 +189,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         tma_load_3d(base + S::W_BYTES, &map_a, &ctl->full[stage], 0, 0, c * KW);
         if ((int)i + 1 == ns) { tile = own_first; c = 0; }
         else if (++c == kc) { c = 0; ++tile; }
-        if (i == 0) TRACE(1);
       }
-      TRACE(2);
       if (*abort_flag) {
         // giving up: let the copies that are still on their way land before the shared memory goes away
         const uint32_t pending = i < (uint32_t)STAGES ? i : (uint32_t)STAGES;
@@ -236,7 +225,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (uint32_t i = 0; i < (uint32_t)n_local; ++i) {
       const uint32_t stage = i % STAGES, phase = (i / STAGES) & 1u;
       if (!dead && !mbar_wait(&ctl->full[stage], phase, abort_flag)) dead = true;
-      if (i == 0 && threadIdx.x == 0) TRACE(3);
       if (!dead) {
         const uint32_t base = ring + stage * S::STAGE_BYTES;
         const uint32_t wbox = base + w_off;
@@ -258,7 +246,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       const bool tile_ends = c == kc - 1;
       const bool share_ends = (int)i == ns - 1;          // the last of this CTA's units of the shared tiles
-      if ((int)i == n_local - 1 && threadIdx.x == 0) TRACE(4);
       if (tile_ends || share_ends) {
         // ---- the tile (or this CTA's share of it) is summed: hand it over ----
         consumer_sync();                                  // the buffer of the tile before is read
@@ -358,7 +345,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) TRACE(5);
   if (threadIdx.x == 0 && ctl->abort_flag) atomicExch(status, 1);
 }
 
@@ -460,10 +446,3 @@ HK_API long long hk_gemm_stream_workspace(int M, int rw) {
   const int mt = M <= 8 ? 1 : M <= 16 ? 2 : 4;
   return (long long)sm_count() * 2 * (16 * rw) * (8 * mt);
 }
-
-#ifdef HK_TRACE
-// Copies the probes of the last launch to the host: out[160][8] nanoseconds.
-HK_API int hk_gemm_stream_trace(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, hk_stream_trace, sizeof(unsigned long long) * 160 * 8);
-}
-#endif

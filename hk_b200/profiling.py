@@ -97,7 +97,6 @@ def main(argv=None) -> int:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--intermediate", type=int, default=12288)
     ap.add_argument("--vocab", type=int, default=151936)
-    ap.add_argument("--cluster", type=int, default=0, help="gemm_smallm: pin the CTAs per cluster that split K (1, 2 or 4)")
     ap.add_argument("--mma", action="store_true", help="attn_prefill: the mma.sync kernel instead of the tcgen05 one")
     ap.add_argument("--one-tile", action="store_true", help="attn_prefill: the tcgen05 kernel with one query tile per CTA")
     ap.add_argument("--row-warps", type=int, default=0, help="gemm_stream: consumer warps across a tile's rows (8, 4, 2 or 1)")
@@ -106,7 +105,6 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     from .csrc import attention_fast, gemm_fast, ops
     gemm_fast._rt_override = a.row_tiles
-    gemm_fast._cs_override = a.cluster
     gemm_fast._stream_ctas = a.ctas
     if a.case == "gemm_tc":
         gemm_fast._tc_bn, gemm_fast._tc_splits = a.bn, a.splits

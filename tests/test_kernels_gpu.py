@@ -398,19 +398,6 @@ def test_gemm_small_m(m, n, k):
     gemm_case("smallm", m, n, k, True, seed=1)
 
 
-@pytest.mark.parametrize("cs", [2, 4])
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 300, 1032), (16, 64, 8192)])
-def test_gemm_small_m_cluster_split_k(cs, m, n, k):
-    # K split over a thread-block cluster, partial sums through distributed shared memory
-    from hk_b200.csrc import gemm_fast
-    gemm_fast._cs_override = cs
-    try:
-        gemm_case("smallm", m, n, k, False)
-        gemm_case("smallm", m, n, k, True, seed=2)
-    finally:
-        gemm_fast._cs_override = 0
-
-
 @pytest.mark.parametrize("rw", [8, 4, 2, 1])
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("n,k", [(16, 64), (300, 192), (1000, 4096), (4096, 12288), (6144, 512), (40, 64), (18992, 128), (2400, 320)])
