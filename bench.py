@@ -141,19 +141,19 @@ def run(args):
     cfg = config_from_dict(shape)
     pk = peaks()
     batches = sorted({1, 8, 64} if not args.quick else {1, 8})
-    max_b = max(batches)
     regions = 1 if args.quick else REGIONS
     per_req = -(-(PROMPT + args.warmup + regions * args.steps + 8) // 64) * 64
     rng = np.random.default_rng(SEED)
     vocab = shape["vocab_size"]
 
-    def make_engine(page):
+    def make_engine(page, batch):
+        """An engine sized for `batch` requests (slots and pages), as a server started for that load would be."""
         t_load = time.time()
-        eng = Engine(config=cfg, random_seed=SEED, dtype="bfloat16", max_tokens=max_b * per_req, page_tokens=page,
-                     max_requests=max_b, max_context=CONTEXT, max_batch_tokens=max(PROMPT, max_b))
+        eng = Engine(config=cfg, random_seed=SEED, dtype="bfloat16", max_tokens=batch * per_req, page_tokens=page,
+                     max_requests=batch, max_context=CONTEXT, max_batch_tokens=max(PROMPT, batch))
         torch.cuda.synchronize()
         print(f"[bench] model ready in {time.time() - t_load:.1f} s ({layers} of {layers_full} layers, {page}-token pages, "
-              f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device)", file=sys.stderr, flush=True)
+              f"{batch} requests, {torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device)", file=sys.stderr, flush=True)
         return eng
 
     def ev():
@@ -232,36 +232,46 @@ def run(args):
     def e2e_point(engine, batch):
         prompts = [rng.integers(0, vocab, PROMPT).tolist() for _ in range(batch)]
         st = GenerationStats()
-        generate_with_engine(engine, prompts, max_new_tokens=args.warmup + args.steps + 1, temperature=0, top_k=0,
+        # as many new tokens as the decode point ran steps (its warm-up included): a tail of a few steps would mostly
+        # time the hand-over from the last prompt portion to decoding
+        generate_with_engine(engine, prompts, max_new_tokens=args.warmup + regions * args.steps + 1, temperature=0, top_k=0,
                              eos_token_ids=(), prefill_chunk=PROMPT, stats=st)
         return {"value": st.decode_tokens / max(st.decode_seconds, 1e-9), "unit": "tokens/s",
                 "h2d_bytes_per_step": st.h2d_bytes_per_step, "d2h_bytes_per_step": st.d2h_bytes_per_step}
 
-    engine = make_engine(PAGE)
-    pre = prefill_point(engine)
-    clocks = ClockSampler()
-    dec = {8: decode_point(engine, 8, clocks)}
-    clock_info = clocks.stop(dec[8]["window"])
-    for bsz in batches:
-        if bsz != 8:
+    import gc
+
+    def drop():
+        gc.collect()                    # an engine and its captured graphs refer to each other
+        torch.cuda.empty_cache()
+
+    dec, e2e = {}, {}
+    pre = clock_info = None
+    for bsz in [8] + [b for b in batches if b != 8]:          # the headline first
+        engine = make_engine(PAGE, bsz)
+        if bsz == 8:
+            pre = prefill_point(engine)
+            clocks = ClockSampler()
+            dec[8] = decode_point(engine, 8, clocks)
+            clock_info = clocks.stop(dec[8]["window"])
+        else:
             dec[bsz] = decode_point(engine, bsz)
-    e2e = {bsz: e2e_point(engine, bsz) for bsz in batches}
+        e2e[bsz] = e2e_point(engine, bsz)
+        e2e[bsz]["of_device_timed"] = e2e[bsz]["value"] / dec[bsz]["tok_s"]
+        engine = None
+        drop()
     points = {f"decode_b{b}": dec[b]["tok_s"] for b in batches if b != 8}
     roof_points = {f"decode_b{b}": dec[b]["roofline"] for b in batches}
     e2e_points = {f"decode_b{b}": e2e[b] for b in batches if b != 8}
-    for b in batches:
-        e2e[b]["of_device_timed"] = e2e[b]["value"] / dec[b]["tok_s"]
     if not args.quick:
         # the same decode points over 64-token pages
-        del engine
-        import gc
-        gc.collect()                    # the engine and its captured graphs refer to each other
-        torch.cuda.empty_cache()
-        engine = make_engine(PAGE_EXTRA)
         for bsz in batches:
+            engine = make_engine(PAGE_EXTRA, bsz)
             d = decode_point(engine, bsz)
             points[f"decode_b{bsz}_page{PAGE_EXTRA}"] = d["tok_s"]
             roof_points[f"decode_b{bsz}_page{PAGE_EXTRA}"] = d["roofline"]
+            engine = None
+            drop()
 
     main = dec[8]
     line = {
@@ -275,7 +285,7 @@ def run(args):
                    "heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
                    "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"], "vocab": vocab,
                    "global_batch": 8, "seq_len": PROMPT, "context": CONTEXT, "page_tokens": PAGE,
-                   "page_tokens_extra_points": PAGE_EXTRA, "regions": regions,
+                   "page_tokens_extra_points": PAGE_EXTRA, "regions": regions, "engine": "one per batch size, sized for it",
                    "parallelism": "1 gpu", "l2": "each step reads >15 GB of weights, larger than L2; no flush",
                    "peaks": pk["source"]},
         "prefill": pre,

@@ -578,6 +578,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int t_end = (it.kv_hi + TT - 1) / TT;
   // All of the above read only what the host wrote before the step (items, block table); the queries and this
   // step's keys and values come from the kernel before.
+  pdl_wait();
   __syncthreads();   // page ids, zeroes and barriers are in place
 
   float o[HD / 8][4];
@@ -726,6 +727,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
   }
   __syncthreads();
+  pdl_launch_dependents();   // the keys are read: the next kernel may move in
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicExch(status, 2);
     return;            // nothing is written
@@ -785,6 +787,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
                                          const int* __restrict__ first, const int* __restrict__ count,
                                          const int* __restrict__ row0, bf16* __restrict__ out, int n_tokens, int H, int G,
                                          int rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (w >= n_tokens * H) return;
@@ -952,7 +956,7 @@ int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* 
   static HkSmemCache allowed = {};
   if (int e = hk_allow_smem(attention_decode_tma_kernel<HD>, smem, allowed)) return e;
   dim3 grid((unsigned)n_items, (unsigned)G);
-  return hk_launch(attention_decode_tma_kernel<HD>, grid, dim3((TW + 1) * 32), smem, s, mk, mv, (const bf16*)q, bt, stride,
+  return hk_launch_pdl(attention_decode_tma_kernel<HD>, grid, dim3((TW + 1) * 32), smem, s, mk, mv, (const bf16*)q, bt, stride,
                        (const Item*)items, (bf16*)out, part_o, part_ml, H, G, pt, box_rows, window, scale_log2, pages_cap, status);
 }
 

@@ -27,6 +27,8 @@ template <typename T, int PER>
 __global__ void embedding_vec_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                      int d, int vocab) {
   constexpr int E = 16 / sizeof(T);   // elements per 16-byte load
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -122,11 +124,13 @@ rms_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, co
   const float4* wv = reinterpret_cast<const float4*>(w);
   const int chunks = d >> 2;
   float4 v[PER], g[PER];
+  pdl_launch_dependents();
 #pragma unroll
   for (int k = 0; k < PER; ++k) {     // the norm's weight does not depend on the kernel before
     const int c = threadIdx.x + k * 256;
     if (c < chunks) g[k] = wv[c];
   }
+  pdl_wait();
   const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
@@ -173,9 +177,9 @@ template <int PER>
 static int rms_norm_vec(const float* x, const float* w, const int* rows, void* out, int out_dtype, int n_out, int d, float eps,
                         cudaStream_t s) {
   if (out_dtype == HK_F32)
-    return hk_launch(rms_norm_vec_kernel<float, PER>, dim3(n_out), dim3(256), 0, s, x, w, rows, (float*)out, d, eps);
+    return hk_launch_pdl(rms_norm_vec_kernel<float, PER>, dim3(n_out), dim3(256), 0, s, x, w, rows, (float*)out, d, eps);
   if (out_dtype == HK_BF16)
-    return hk_launch(rms_norm_vec_kernel<bf16, PER>, dim3(n_out), dim3(256), 0, s, x, w, rows, (bf16*)out, d, eps);
+    return hk_launch_pdl(rms_norm_vec_kernel<bf16, PER>, dim3(n_out), dim3(256), 0, s, x, w, rows, (bf16*)out, d, eps);
   return HK_ERR_UNSUPPORTED;
 }
 
@@ -222,6 +226,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
     int write_kv, const float* __restrict__ bias, int pairing) {
   __shared__ float buf[QKR_WARPS][QKR_MAX_HD];
+  pdl_launch_dependents();
+  pdl_wait();
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int heads_total = H + (write_kv ? 2 * G : 0);
   long long item = (long long)blockIdx.x * QKR_WARPS + wid;
@@ -288,6 +294,8 @@ qk_norm_rope_kv_write_vec_kernel(
     const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int hd, int page_tokens,
     int write_kv, const float* __restrict__ bias, int pairing) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int heads_total = H + (write_kv ? 2 * G : 0);
   const long long item = (long long)blockIdx.x * QKV_WARPS + wid;
@@ -380,11 +388,11 @@ HK_API int hk_qk_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, co
   if (hd <= 128 && (hd & 3) == 0 && (rot & 7) == 0 && aligned) {
     unsigned vblocks = (unsigned)((items + QKV_WARPS - 1) / QKV_WARPS);
     if (dtype == HK_F32)
-      return hk_launch(qk_norm_rope_kv_write_vec_kernel<float>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (float*)q_out,
+      return hk_launch_pdl(qk_norm_rope_kv_write_vec_kernel<float>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (float*)q_out,
                        q_w, k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (float*)k_pages,
                        (float*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
     if (dtype == HK_BF16)
-      return hk_launch(qk_norm_rope_kv_write_vec_kernel<bf16>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
+      return hk_launch_pdl(qk_norm_rope_kv_write_vec_kernel<bf16>, dim3(vblocks), dim3(QKV_WARPS * 32), 0, s, qkv, (bf16*)q_out, q_w,
                        k_w, eps, cos_t, sin_t, rot, positions, slot_of_token, block_table, table_stride, (bf16*)k_pages,
                        (bf16*)v_pages, n, H, G, hd, page_tokens, write_kv, bias, pairing);
     return HK_ERR_UNSUPPORTED;
@@ -419,6 +427,8 @@ HK_API int hk_add_bias(float* out, const float* bias, int n, int N, void* stream
 // `block` gates followed by the matching `block` ups (block == F: all gates, then all ups).
 template <typename TO>
 __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block) {
+  pdl_launch_dependents();
+  pdl_wait();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   long long t = i / F;
