@@ -162,47 +162,6 @@ def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
     return True
 
 
-FFN_FUSED_M = 16      # the most rows the one-kernel feed-forward takes
-_ffn_sync = {}
-_ffn_ctas = 0         # tests may run fewer CTAs than SMs
-
-
-FFN_FUSED_AUTO = False     # measured: 4.47 ms a decode step at batch 8 against 4.25 with the three kernels (see below)
-
-
-def ffn_fused_wanted(M: int, d: int, F: int) -> bool:
-    """The feed-forward as one streaming kernel (norm, gate/up with SwiGLU, down with the residual sum), for decode
-    batches of up to 16 rows whose two products the streaming kernel would take anyway.  It is correct and streams
-    its phases at 5.4-6 TB/s, but the two gates between its phases (every CTA waits for the slowest one's norm row and
-    for the slowest one's last gate/up tile, about 5 and 4 microseconds with HBM idle) cost what the two launches it
-    saves cost, so the three kernels stay the default; `ops.force(gemm="stream")` still reaches it."""
-    return FFN_FUSED_AUTO and M <= FFN_FUSED_M and d % 64 == 0 and F % 128 == 0 and stream_wanted(M, 2 * F, d) and stream_wanted(M, d, F)
-
-
-def run_ffn_fused(residual, norm_w, eps: float, w_gate_up, w_down, xb, h) -> bool:
-    """residual (fp32 [M, d]) += down(silu(gate) * up) of rmsnorm(residual); xb (bf16 [M, d]) and h (bf16 [M, F]) are
-    scratch.  False when the kernel refuses the sizes (or its buffers cannot be made now: a stream is capturing)."""
-    from . import ops
-    M, d = residual.shape
-    F = w_down.shape[1]
-    lib = build.load("gemm_stream")
-    scratch = _stream_buffers(residual.device, lib)
-    key = residual.device.index or 0
-    if key not in _ffn_sync:
-        if torch.cuda.is_current_stream_capturing():
-            return False
-        _ffn_sync[key] = torch.zeros(4, dtype=torch.int32, device=residual.device)
-    if scratch is None:
-        return False
-    ws, ct = scratch
-    code = lib.hk_ffn_stream(_ptr(residual), _ptr(norm_w), ctypes.c_float(eps), _ptr(w_gate_up), _ptr(w_down), _ptr(xb), _ptr(h),
-                             M, d, F, _ptr(ws), _ptr(ct), _ptr(_ffn_sync[key]), _ptr(status_flag(residual.device)), _ffn_ctas, _stream())
-    if code == _UNSUPPORTED:
-        return False
-    ops._check(code, "feed-forward (one streaming kernel)")
-    return True
-
-
 def _tc_partial(lib, M: int, N: int, splits: int, device):
     """Scratch for the partial sums of `splits` K slices (None without slices)."""
     if splits <= 1:

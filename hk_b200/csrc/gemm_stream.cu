@@ -161,7 +161,7 @@ __device__ __forceinline__ Sched make_sched(int n_tiles, int kc, long long P, lo
 
 // The consumer warps' side of one product: multiplies this CTA's units as their stages fill (unit i of the product
 // is stage (i_base + i) % STAGES of the ring) and hands every tile, or share of a tile, over.
-template <int RW, int MT, int EPI, bool LAST_PRODUCT = true>
+template <int RW, int MT, int EPI>
 __device__ __forceinline__ void consume_units(const Sched& sc, uint32_t i_base, uint32_t ring, Control* ctl, float* tile_buf,
                                               void* __restrict__ out, int M, int N, long long ldo, float* __restrict__ workspace,
                                               int* __restrict__ counters) {
@@ -213,7 +213,7 @@ __device__ __forceinline__ void consume_units(const Sched& sc, uint32_t i_base, 
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->empty[stage]);
     }
-    if (LAST_PRODUCT && (int)i == n_local - 1) pdl_launch_dependents();   // this CTA's weights are read: the next kernel may move in
+    if ((int)i == n_local - 1) pdl_launch_dependents();   // this CTA's weights are read: the next kernel may move in
     const bool tile_ends = c == kc - 1;
     const bool share_ends = (int)i == ns - 1;          // the last of this CTA's units of the shared tiles
     if (tile_ends || share_ends) {
@@ -447,229 +447,6 @@ int launch_epi(int epilogue, const void* a, const void* w, void* out, int M, int
 }
 
 
-// ---- the feed-forward of a decode step as ONE kernel -----------------------------------------------------------
-// xb = rmsnorm(residual) ; h = silu(xb Wg^T) * (xb Wu^T) ; residual += h Wd^T, for M <= 16 rows.  Three kernels
-// each pay a launch, the time until their first weights land and a tail in which the last tiles are handed over
-// while HBM idles.  Here the producer warp never stops: it streams the gate/up weights and then the down weights
-// through the same ring, and only the *activation* tile of a stage waits for the phase before (a counter in global
-// memory that every CTA bumps when its share of a phase is written; one CTA per SM, so all of them are resident).
-// While the CTAs meet at such a gate, the ring already holds the next phase's first weights.
-//
-//   phase 0   CTA r < M normalises row r of the residual into xb (bf16); every CTA then bumps gate 0
-//   phase 1   units of [2F, d] (paired gate/up layout), silu(gate) * up epilogue into h (bf16); gate 1
-//   phase 2   units of [d, F], added onto the residual
-// `sync` holds the two gates and an exit count; the CTA that leaves last sets them back to zero for the next launch.
-constexpr uint32_t GATE_LIMIT = 1u << 19;
-
-struct alignas(64) FfnArgs {
-  CUtensorMap map_x, map_wgu, map_h, map_wd;
-  const float* norm_w;
-  float* residual;
-  bf16* xb;
-  bf16* h;
-  float* workspace;
-  int* counters;
-  unsigned int* sync;
-  int* status;
-  float eps;
-  int M, d, F;
-};
-
-__device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-template <int MT>
-__global__ void __launch_bounds__(NUM_THREADS, 1) ffn_stream_kernel(const __grid_constant__ FfnArgs args) {
-  constexpr int RW = 1;
-  using S = Shape<RW, MT>;
-  constexpr int BN = S::BN, BK = S::BK, KW = S::KW, STAGES = S::STAGES;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* after = smem_raw + (ring - smem_u32(smem_raw)) + (size_t)STAGES * S::STAGE_BYTES;
-  float* tile_buf = reinterpret_cast<float*>(after);
-  Control* ctl = reinterpret_cast<Control*>(after + S::TILE_FLOATS * 4);
-  volatile int* abort_flag = &ctl->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned int P = gridDim.x;
-  const int M = args.M, d = args.d, F = args.F;
-  const Sched s1 = make_sched(2 * F / BN, (d + BK - 1) / BK, P, blockIdx.x);
-  const Sched s2 = make_sched((d + BN - 1) / BN, (F + BK - 1) / BK, P, blockIdx.x);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&ctl->full[s], 2);               // the weights' copy and the activations' copy announce themselves apart
-      mbar_init(&ctl->empty[s], CONSUMERS);
-    }
-    ctl->abort_flag = 0;
-    ctl->last = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-
-  if (warp == CONSUMERS) {
-    // ---- producer ----
-    // One thread, and it has a stage to fill every third of a microsecond: the loop below is kept to a few dozen
-    // instructions per unit on scalars.  A phase's units are sent for in order; while its gate is closed only their
-    // weights go out (the activations of units [ai, i) are owed), a look at the gate costs a trip to L2 and is taken
-    // every fourth unit, and once the ring holds nothing but owed stages the thread waits at the gate.
-    if (lane == 0) {
-      bool alive = true;
-      auto run_phase = [&](const Sched& sc, const CUtensorMap* map_w, const CUtensorMap* map_a, const unsigned int* gate_word,
-                           uint32_t i_base, bool swiglu) {
-        const int n = sc.n_local, kc = sc.kc, ns = sc.ns, own_first = sc.own_first;
-        int tile = ns > 0 ? (int)(sc.u0 / kc) : own_first, c = ns > 0 ? (int)(sc.u0 % kc) : 0;
-        int ac = c, ai = 0;                         // the activations owed: units [ai, i), unit ai reads K chunk ac
-        bool open = false;
-        auto look = [&](bool block) {
-          for (uint32_t spin = 0; spin < (block ? GATE_LIMIT : 1u); ++spin) {
-            if (ld_acquire(gate_word) >= P) {
-              asm volatile("fence.proxy.async;" ::: "memory");   // the other CTAs' stores, before this thread's TMA reads
-              open = true;
-              return;
-            }
-            if (block) {
-              if ((spin & 15u) == 15u && *abort_flag) { alive = false; return; }
-              __nanosleep(64);
-            }
-          }
-          if (block) { *abort_flag = 1; alive = false; }
-        };
-        auto pay = [&](int upto) {                  // sends for the owed activations of units [ai, upto)
-          for (; ai < upto; ++ai) {
-            const uint32_t st = (i_base + (uint32_t)ai) % STAGES;
-            mbar_expect_tx(&ctl->full[st], S::A_BYTES);
-            tma_load_3d(ring + st * S::STAGE_BYTES + S::W_BYTES, map_a, &ctl->full[st], 0, 0, ac * KW);
-            if (ai + 1 == ns) ac = 0;
-            else if (++ac == kc) ac = 0;
-          }
-        };
-        for (int i = 0; i < n && alive; ++i) {
-          const uint32_t gi = i_base + (uint32_t)i, stage = gi % STAGES, phase = (gi / STAGES) & 1u;
-          if (!open) {
-            if (ai + STAGES <= i) look(true);
-            else if ((i & 3) == 3) look(false);
-            if (!alive) break;
-            if (open) pay(i);
-          }
-          if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
-          const uint32_t base = ring + stage * S::STAGE_BYTES;
-          const int r0 = swiglu ? tile_row<BN, EPI_SWIGLU>(tile, 0) : tile_row<BN, EPI_ADD>(tile, 0);
-          const int r1 = swiglu ? tile_row<BN, EPI_SWIGLU>(tile, 1) : tile_row<BN, EPI_ADD>(tile, 1);
-          if (open) {
-            mbar_arrive(&ctl->full[stage]);
-            mbar_expect_tx(&ctl->full[stage], S::STAGE_BYTES);
-            tma_load_3d(base, map_w, &ctl->full[stage], 0, r0, c * KW);
-            tma_load_3d(base + S::W_HALF, map_w, &ctl->full[stage], 0, r1, c * KW);
-            tma_load_3d(base + S::W_BYTES, map_a, &ctl->full[stage], 0, 0, c * KW);
-            ai = i + 1;
-          } else {
-            mbar_expect_tx(&ctl->full[stage], S::W_BYTES);
-            tma_load_3d(base, map_w, &ctl->full[stage], 0, r0, c * KW);
-            tma_load_3d(base + S::W_HALF, map_w, &ctl->full[stage], 0, r1, c * KW);
-          }
-          if (i + 1 == ns) { tile = own_first; c = 0; }
-          else if (++c == kc) { c = 0; ++tile; }
-          if (open) ac = c;
-        }
-        if (alive && !open && ai < n) {
-          look(true);
-          if (alive) pay(n);
-        }
-      };
-      run_phase(s1, &args.map_wgu, &args.map_x, args.sync + 0, 0u, true);
-      if (alive) run_phase(s2, &args.map_wd, &args.map_h, args.sync + 1, (uint32_t)s1.n_local, false);
-      if (*abort_flag) {
-        // giving up: let the copies that are still on their way land before the shared memory goes away (a stage
-        // whose activations were never sent for does not complete; the tries are bounded)
-        for (int st = 0; st < STAGES; ++st)
-          for (uint32_t spin = 0; spin < (1u << 14); ++spin)
-            if (mbar_try_wait(&ctl->full[st], 0u) || mbar_try_wait(&ctl->full[st], 1u)) break;
-      }
-    }
-  } else {
-    // ---- consumers ----
-    const int tid = threadIdx.x;
-    // phase 0: row r of the residual, normalised, for CTA r (and r + P, ...)
-    for (int r = blockIdx.x; r < M; r += (int)P) {
-      const float* x = args.residual + (size_t)r * d;
-      // d is a multiple of 64: 16-byte loads, four of them under way per thread
-      const float4* x4 = reinterpret_cast<const float4*>(x);
-      const int n4 = d >> 2;
-      float ss = 0.f;
-      for (int k0 = tid; k0 < n4; k0 += 4 * CONSUMERS * 32) {
-        float4 v[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int k = k0 + u * CONSUMERS * 32;
-          v[u] = k < n4 ? __ldcg(x4 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
-      }
-      ss = warp_sum(ss);
-      consumer_sync();
-      if (lane == 0) tile_buf[warp] = ss;
-      consumer_sync();
-      float tot = 0.f;
-#pragma unroll
-      for (int wv = 0; wv < CONSUMERS; ++wv) tot += tile_buf[wv];
-      const float inv = 1.0f / sqrtf(tot / (float)d + args.eps);
-      const float4* w4 = reinterpret_cast<const float4*>(args.norm_w);
-      for (int k0 = tid; k0 < n4; k0 += 4 * CONSUMERS * 32) {
-        float4 v[4], g[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int k = k0 + u * CONSUMERS * 32;
-          v[u] = k < n4 ? __ldcg(x4 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-          g[u] = k < n4 ? __ldg(w4 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int k = k0 + u * CONSUMERS * 32;
-          if (k < n4) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * inv * g[u].x, v[u].y * inv * g[u].y);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * inv * g[u].z, v[u].w * inv * g[u].w);
-            *reinterpret_cast<uint2*>(args.xb + (size_t)r * d + 4 * (size_t)k) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-          }
-        }
-      }
-    }
-    __threadfence();
-    consumer_sync();
-    if (tid == 0) atomicAdd(args.sync + 0, 1u);
-    consume_units<RW, MT, EPI_SWIGLU, false>(s1, 0u, ring, ctl, tile_buf, args.h, M, 2 * F, (long long)F, args.workspace, args.counters);
-    __threadfence();
-    consumer_sync();
-    if (tid == 0) atomicAdd(args.sync + 1, 1u);
-    consume_units<RW, MT, EPI_ADD>(s2, (uint32_t)s1.n_local, ring, ctl, tile_buf, args.residual, M, d, (long long)d, args.workspace,
-                                   args.counters + s1.n_tiles);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (ctl->abort_flag) atomicExch(args.status, 1);
-    __threadfence();
-    if (atomicAdd(args.sync + 2, 1u) == P - 1) {          // the last CTA out: nobody reads the gates any more
-      args.sync[0] = 0;
-      args.sync[1] = 0;
-      args.sync[2] = 0;
-    }
-  }
-}
-
-template <int MT>
-int launch_ffn(const FfnArgs& args, int max_ctas, cudaStream_t s) {
-  using S = Shape<1, MT>;
-  static HkSmemCache allowed = {};
-  if (int e = hk_allow_smem(ffn_stream_kernel<MT>, (size_t)S::SMEM, allowed)) return e;
-  int grid = sm_count();
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  return hk_launch(ffn_stream_kernel<MT>, dim3((unsigned)grid), dim3(NUM_THREADS), (size_t)S::SMEM, s, args);
-}
-
 }  // namespace
 
 // out = a w^T for M <= 32.  epilogue 0: out fp32 [M, N] stored; 1: out fp32 [M, N] +=; 2: out bf16 [M, N/2] =
@@ -700,40 +477,4 @@ HK_API int hk_gemm_stream(const void* a, const void* w, void* out, int M, int N,
 HK_API long long hk_gemm_stream_workspace(int M, int rw) {
   const int mt = M <= 8 ? 1 : M <= 16 ? 2 : 4;
   return (long long)sm_count() * 2 * (16 * rw) * (8 * mt);
-}
-
-// The feed-forward of a decode step in one launch: xb = rmsnorm(residual, norm_w, eps) (bf16 [M, d], scratch);
-// h = silu(gate) * up of xb w_gate_up^T (bf16 [M, F], scratch; w_gate_up [2F, d] in the paired layout);
-// residual += h w_down^T (w_down [d, F]).  M <= 16.  workspace and counters as for hk_gemm_stream (counters: one
-// int per tile of 16 rows of BOTH weights); sync: three zeroed uints (left zero); status: set to 1 by a timed-out
-// wait.  All buffers belong to one stream of launches.  max_ctas: 0 = one CTA per SM (more would not be resident
-// together; the gates between the phases need that).
-// Refuses (HK_ERR_UNSUPPORTED) M > 16, d % 64 != 0, F % 128 != 0, operands not 16-byte aligned.
-HK_API int hk_ffn_stream(float* residual, const float* norm_w, float eps, const void* w_gate_up, const void* w_down, void* xb,
-                         void* h, int M, int d, int F, float* workspace, int* counters, unsigned int* sync, int* status,
-                         int max_ctas, void* stream) {
-  if (M <= 0) return 0;
-  if (M > 16 || d <= 0 || F <= 0 || (d & 63) || (F & 127)) return HK_ERR_UNSUPPORTED;
-  if (((uintptr_t)w_gate_up & 15) || ((uintptr_t)w_down & 15) || ((uintptr_t)xb & 15) || ((uintptr_t)h & 15)) return HK_ERR_UNSUPPORTED;
-  if (!residual || !norm_w || !workspace || !counters || !sync || !status) return HK_ERR_UNSUPPORTED;
-  const int mt = M <= 8 ? 1 : 2;
-  FfnArgs args;
-  constexpr int KW = 8;
-  if (!make_map(&args.map_x, xb, M, d, 8 * mt, KW) || !make_map(&args.map_wgu, w_gate_up, 2 * F, d, 8, KW) ||
-      !make_map(&args.map_h, h, M, F, 8 * mt, KW) || !make_map(&args.map_wd, w_down, d, F, 8, KW))
-    return HK_ERR_UNSUPPORTED;
-  args.norm_w = norm_w;
-  args.residual = residual;
-  args.xb = (bf16*)xb;
-  args.h = (bf16*)h;
-  args.workspace = workspace;
-  args.counters = counters;
-  args.sync = sync;
-  args.status = status;
-  args.eps = eps;
-  args.M = M;
-  args.d = d;
-  args.F = F;
-  cudaStream_t s = (cudaStream_t)stream;
-  return mt == 1 ? launch_ffn<1>(args, max_ctas, s) : launch_ffn<2>(args, max_ctas, s);
 }

@@ -193,27 +193,6 @@ def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, bloc
     swiglu(gu, out, block)
 
 
-def ffn_fused(residual: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_paired: torch.Tensor, w_down: torch.Tensor,
-              block: int) -> bool:
-    """residual[M, d] (float32) += (silu(gate) * up)(rmsnorm(residual) w_paired^T) w_down^T in ONE kernel, for a small
-    decode batch in bfloat16 with the paired gate/up layout.  Returns False (and does nothing) when that kernel does
-    not take the sizes; the caller then runs norm, the two products and SwiGLU one after the other."""
-    if _forced["gemm"] not in (None, "stream") or w_paired.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16:
-        return False
-    from . import gemm_fast
-    M, d = residual.shape
-    F = w_down.shape[1]
-    if block != gemm_fast.PAIR or tuple(w_paired.shape) != (2 * F, d) or w_down.shape[0] != d:
-        return False
-    if _forced["gemm"] is None and not gemm_fast.ffn_fused_wanted(M, d, F):
-        return False
-    _need(residual, "residual", torch.float32, 2)
-    _need(norm_weight, "norm_weight", torch.float32, 1)
-    xb = torch.empty((M, d), dtype=torch.bfloat16, device=residual.device)
-    h = torch.empty((M, F), dtype=torch.bfloat16, device=residual.device)
-    return gemm_fast.run_ffn_fused(residual, norm_weight, eps, w_paired, w_down, xb, h)
-
-
 # ---- per-head norm + rotation + cache write ---------------------------------------------
 
 

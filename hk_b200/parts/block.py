@@ -27,10 +27,6 @@ class PreNormBlock(Part):
         xb = torch.empty(residual.shape, dtype=ctx.precision.compute, device=residual.device)
         self.mixer_norm.forward(residual, xb)
         self.mixer.forward(xb, residual, ctx, caches[0], write_cache)
-        # a feed-forward may take the norm before it into its own kernel (it says so by the call's result)
-        fused = getattr(self.feed_forward, "forward_from_residual", None)
-        if fused is not None and fused(self.ffn_norm, residual, ctx):
-            return
         self.ffn_norm.forward(residual, xb)
         self.feed_forward.forward(xb, residual, ctx)
 

@@ -45,14 +45,6 @@ class SwiGLUFeedForward(Part):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"]
 
-    def forward_from_residual(self, norm, residual: torch.Tensor, ctx) -> bool:
-        """The block's norm and this feed-forward in one kernel, where there is one for the sizes (small decode batches
-        in bfloat16): residual += ffn(norm(residual)).  False: nothing was done, the block runs norm and `forward`."""
-        from .norm import RMSNorm
-        if self.w_gate_up.dtype != torch.bfloat16 or type(norm) is not RMSNorm or norm.weight is None:
-            return False
-        return ops.ffn_fused(residual, norm.weight, norm.eps, self.w_gate_up, self.w_down, self.block)
-
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         h = torch.empty((xb.shape[0], self.F), dtype=xb.dtype, device=xb.device)
         ops.gemm_swiglu(xb, self.w_gate_up, h, self.block)

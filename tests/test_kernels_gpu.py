@@ -460,39 +460,6 @@ def test_gemm_stream_swiglu_epilogue(rw, m, f, k):
     close(out, want, torch.bfloat16, atol=2e-3)
 
 
-@pytest.mark.parametrize("ctas", [0, 1, 5, 37])
-@pytest.mark.parametrize("m,d,f", [(1, 64, 128), (8, 192, 384), (5, 4096, 12288), (16, 1024, 2560), (9, 320, 1152), (3, 5120, 1536)])
-def test_feed_forward_in_one_kernel(m, d, f, ctas):
-    # norm, gate/up with SwiGLU and down with the residual sum in one streaming kernel with gates between the phases;
-    # fewer CTAs move the places where tiles are handed over and let one CTA own several rows of the norm
-    from hk_b200.csrc import gemm_fast
-    g = torch.Generator().manual_seed(m + d + f)
-    res0 = torch.randn(m, d, generator=g) * 2
-    nw = (1 + 0.2 * torch.randn(d, generator=g)).float()
-    gate = (torch.randn(f, d, generator=g) / math.sqrt(d)).to(torch.bfloat16)
-    up = (torch.randn(f, d, generator=g) / math.sqrt(d)).to(torch.bfloat16)
-    down = (torch.randn(d, f, generator=g) / math.sqrt(f)).to(torch.bfloat16)
-    eps = 1e-5
-    gemm_fast._ffn_ctas = ctas
-    try:
-        outs = []
-        for rep in range(2):
-            res = res0.clone().to(DEV)
-            with ops().force(gemm="stream"):
-                assert ops().ffn_fused(res, nw.to(DEV), eps, gemm_fast.pair_gate_up(gate, up).to(DEV), down.to(DEV), gemm_fast.PAIR)
-            outs.append(res)
-        gemm_fast.check_status(torch.device(DEV))
-    finally:
-        gemm_fast._ffn_ctas = 0
-    assert torch.equal(outs[0], outs[1])                         # fixed order of the partial sums
-    assert int(gemm_fast._ffn_sync[0].abs().sum()) == 0         # the gates are back at zero
-    # reference with the kernel's roundings: xb and h in bfloat16
-    xb = ref_ops.rms_norm(res0, nw, eps).to(torch.bfloat16)
-    h = ref_ops.swiglu(torch.cat([ref_ops.gemm(xb, gate), ref_ops.gemm(xb, up)], dim=1)).to(torch.bfloat16)
-    want = res0.double() + ref_ops.gemm(h, down)
-    close(outs[0], want, torch.float32, atol=3e-3, rtol=3e-3)
-
-
 def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
     a = torch.randn(4, 70).to(torch.bfloat16).to(DEV)      # K % 8 != 0
     w = torch.randn(9, 70).to(torch.bfloat16).to(DEV)
