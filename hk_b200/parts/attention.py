@@ -108,9 +108,14 @@ class GQAAttention(Part):
         H, G, hd = self.H, self.G, self.hd
         tc = attention_fast.tc_prefill_supported(hd, H // G) and ops.forced("attention") != "flash_cp"
         rows = 128 if tc else 64
-        # portions of more than 128 rows take the kernel with two query tiles per CTA, where the pages allow it
-        if tc and max(ctx.q_lens) * (H // G) > 128 and attention_fast.tc2_prefill_supported(hd, H // G, ctx.page_tokens):
-            rows = 256
+        # the kernel with two query tiles per CTA is the faster one per row, but halves the number of work items: it
+        # is taken when its items still fill the SMs (measured on the 8B layer: equal at 1,024 prompt tokens = 128
+        # items, 1.6 times faster at 2,048, 1.3 times slower at 512), where the pages allow it
+        if tc and attention_fast.tc2_prefill_supported(hd, H // G, ctx.page_tokens):
+            group = H // G
+            items = G * sum(-(-(int(q) * group) // 256) for q in ctx.q_lens if int(q) * group > 128)
+            if items * 20 >= self._sm_count * 17:
+                rows = 256
         fixed = attention_fast.decode_splits(ctx.n_tokens, G, self._sm_count) if ctx.fixed_shape else 0
         got = attention_fast.plan_arrays(ctx.slots, ctx.q_starts, ctx.q_lens, ctx.start_positions, ctx.n_tokens,
                                          self.window or 0, H, G, self._sm_count, fixed_splits=fixed,

@@ -104,3 +104,25 @@ def test_decode_plan_in_array_arithmetic_equals_the_general_loop():
                 b = max(a, min(kv_hi, start + (s + 1) * chunk))
                 assert (int(items[i, s, 4]), int(items[i, s, 5])) == (a, b)
         assert info.n_parts == B * splits and merge.shape == (3, B)
+
+
+def test_the_attention_part_takes_two_query_tiles_only_when_their_items_fill_the_gpu():
+    """The mixer's `step_tables` picks the rows per work item: 256 (two query tiles per CTA) when those items are
+    about as many as the SMs, 128 below that, and never where the pages do not suit the TMA boxes."""
+    from hk_b200.engine.context import StepContext
+    from hk_b200.parts import GQAAttention
+    part = GQAAttention(4096, 32, 8, 128, "a.", qk_norm_eps=None, position=None)
+    part._sm_count = 148
+    part._tables_key = ("attention", 32, 8, 128, 0)
+
+    def rows_per_item(q_lens, page_tokens=16):
+        starts = list(np.cumsum([0] + q_lens[:-1]))
+        ctx = StepContext(None, sum(q_lens), None, None, None, list(range(len(q_lens))), [int(s) for s in starts], q_lens,
+                          [0] * len(q_lens), page_tokens=page_tokens)
+        return part.step_tables(ctx).info.nw
+
+    assert rows_per_item([2048]) == 16 and rows_per_item([1024]) == 16     # 256 and 128 items of 256 rows
+    assert rows_per_item([512]) == 8 and rows_per_item([960]) == 8         # 64 and 120 items: one tile per CTA fills more SMs
+    assert rows_per_item([512, 512]) == 16 and rows_per_item([700, 333]) == 16
+    assert rows_per_item([2048], page_tokens=12) == 8                        # pages that are no 16 * 2^n tokens
+    assert rows_per_item([1] * 8) == 1                                      # decode
