@@ -588,28 +588,28 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (warp == TW) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
-      const int boxes = TT / box_rows;
-      const uint32_t box_bytes = (uint32_t)box_rows * HD * 2;
-      for (int t = t_begin; t < t_end; ++t) {
-        const int n = t - t_begin;
-        const int stage = n % TS;
-        if (n >= TS && !mbar_wait_bounded(&empty[stage], (uint32_t)((n / TS - 1) & 1), abort_flag)) break;
-        uint32_t bytes = 0;
-        for (int b = 0; b < boxes; ++b) {
-          const int j = t * TT + b * box_rows;
-          const int pi = j / page_tokens - page_lo;
-          if (j < it.kv_hi && j + box_rows > it.kv_lo && pi >= 0 && pi < n_pages && pages[pi] >= 0) bytes += 2u * box_bytes;
-        }
-        mbar_expect_tx(&full[stage], bytes);
-        for (int b = 0; b < boxes; ++b) {
-          const int j = t * TT + b * box_rows;
-          const int pi = j / page_tokens - page_lo;
-          if (!(j < it.kv_hi && j + box_rows > it.kv_lo && pi >= 0 && pi < n_pages && pages[pi] >= 0)) continue;
-          const int grow = (pages[pi] * G + g) * page_tokens + (j % page_tokens);    // row of the [rows, HD] view
-          tma_load_3d(kbuf + stage * TILE_BYTES + b * box_bytes, &map_k, &full[stage], 0, grow, 0);
-          tma_load_3d(vbuf + stage * TILE_BYTES + b * box_bytes, &map_v, &full[stage], 0, grow, 0);
-        }
+    // One lane per box: lanes [0, boxes) bring the K boxes of a tile, lanes [boxes, 2 * boxes) the V boxes (with
+    // 16-token pages a tile is eight copies of 4 KB: issued by one lane they were the kernel's bound).
+    const int boxes = TT / box_rows;
+    const uint32_t box_bytes = (uint32_t)box_rows * HD * 2;
+    const bool is_v = lane >= boxes;
+    const int b = is_v ? lane - boxes : lane;
+    for (int t = t_begin; t < t_end; ++t) {
+      const int n = t - t_begin;
+      const int stage = n % TS;
+      int ok = 1;
+      if (n >= TS && lane == 0) ok = mbar_wait_bounded(&empty[stage], (uint32_t)((n / TS - 1) & 1), abort_flag) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int j = t * TT + b * box_rows;
+      const int pi = j / page_tokens - page_lo;
+      const bool wanted = lane < 2 * boxes && j < it.kv_hi && j + box_rows > it.kv_lo && pi >= 0 && pi < n_pages && pages[pi] >= 0;
+      const unsigned mask = __ballot_sync(0xffffffffu, wanted);
+      if (lane == 0) mbar_expect_tx(&full[stage], (uint32_t)__popc(mask) * box_bytes);
+      __syncwarp();
+      if (wanted) {
+        const int grow = (pages[pi] * G + g) * page_tokens + (j % page_tokens);    // row of the [rows, HD] view
+        tma_load_3d((is_v ? vbuf : kbuf) + stage * TILE_BYTES + b * box_bytes, is_v ? &map_v : &map_k, &full[stage], 0, grow, 0);
       }
     }
   } else {
