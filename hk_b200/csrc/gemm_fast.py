@@ -69,24 +69,41 @@ def row_tiles(M: int, N: int, device) -> int:
     return _rt_override or 1
 
 
-_tc_bn = 0            # tests and tuning runs may pin the tile width (128 or 256) ...
+_tc_bn = 0            # tests and tuning runs may pin the tile width (a multiple of 16 up to 256) ...
 _tc_splits = 0        # ... and the number of K slices of the tcgen05 kernel
+TC_TILE_FIXED = 150   # a tile's fixed cost in columns: tiles of 128 measured 30-45 % slower per flop than tiles of 256
 
 
-def tc_config(M: int, N: int, K: int, sms: int, bn: int = 0):
-    """Tile width and number of K slices for the tcgen05 kernel.  Wide tiles when they still fill half
-    the SMs; with fewer output tiles than SMs (few rows: decode batches, narrow outputs) K is cut into
-    slices so that every SM streams a share of the weights.  (A finer cost model that also weighed wave
-    tails chose more slices and measured slower: the second kernel that adds the slices has a fixed cost.)"""
+def tc_config(M: int, N: int, K: int, sms: int, swiglu: bool = False):
+    """Tile width (a multiple of 16, of 32 with the SwiGLU epilogue) and number of K slices for the tcgen05 kernel.
+    Many rows (prefill): the width, from 256 down to 192, whose tiles leave the least of the last wave of SMs
+    empty, a tile costing its width plus a fixed part.  Few output tiles (decode batches, narrow outputs):
+    with the SwiGLU epilogue the widest tile that gives every SM one (no slices: the epilogue cannot run on partial
+    sums without a second kernel); else 128- or 256-wide tiles with K cut into slices so that every SM streams a
+    share of the weights.  (A finer cost model that also weighed wave tails chose more slices and measured slower:
+    the second kernel that adds the slices has a fixed cost.)"""
     m_tiles = -(-M // 128)
-    if bn == 0 and _tc_bn:
+    step = 32 if swiglu else 16
+    k_blocks = -(-K // 64)
+    if _tc_bn:
         bn = _tc_bn
-    if bn == 0:
+    elif m_tiles * -(-N // 256) >= sms:
+        best = None
+        for cand in range(256, 191, -step):
+            waves = -(-(m_tiles * -(-N // cand)) // sms)
+            cost = waves * (cand + TC_TILE_FIXED)
+            if best is None or cost < best[0]:
+                best = (cost, cand)
+        bn = best[1]
+    elif swiglu and m_tiles == 1:
+        bn = min(256, max(32, -(-N // sms + step - 1) // step * step))       # the narrowest tile width that needs one wave
+        while bn < 256 and -(-N // bn) > sms:
+            bn += step
+    else:
         bn = 256 if N >= 256 and m_tiles * -(-N // 256) >= sms // 2 else 128
     tiles = m_tiles * -(-N // bn)
-    k_blocks = -(-K // 64)
     splits = 1
-    if tiles < sms:
+    if tiles < sms and not (swiglu and (N // 2) % (bn // 2)):
         splits = max(1, min(sms // tiles, k_blocks // 8))
     if _tc_splits:
         splits = min(_tc_splits, k_blocks)
@@ -142,7 +159,7 @@ def stream_wanted(M: int, N: int, K: int) -> bool:
 
 
 def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
-    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up over the paired layout."""
+    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up over w = [gate rows | up rows]."""
     from . import ops
     M, K = a.shape
     N = w.shape[0]
@@ -203,37 +220,27 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     return True
 
 
-def run_swiglu(a, w_paired, out, choice: Optional[str] = None) -> bool:
-    """out (bf16 [M, F]) = silu(gate) * up of a w^T, for a weight laid out [128 gate | 128 up] per
-    256 rows (see `pair_gate_up`), in the epilogue of the streaming kernel (few rows) or of the tcgen05
-    kernel; False when they refuse."""
+def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None) -> bool:
+    """out (bf16 [M, F]) = silu(gate) * up of a w^T for w = [F gate rows | F up rows], in the epilogue of the
+    streaming kernel (few rows) or of the tcgen05 kernel; False when they refuse."""
     from . import ops
     M, K = a.shape
-    N = w_paired.shape[0]
-    if not _aligned(a, w_paired) or N % 256 or out.shape[1] % 8:
+    N = w_gate_up.shape[0]
+    if not _aligned(a, w_gate_up) or N % 2:
         return False
     if choice == "stream" or (choice is None and stream_wanted(M, N, K)):
-        if run_stream(a, w_paired, out, 2, out.shape[1]):
+        if N % (16 * stream_row_warps(N, _sms(a.device))) == 0 and run_stream(a, w_gate_up, out, 2, out.shape[1]):
             return True
         if choice == "stream":
             return False
     if choice is None and M <= SMALL_M_AUTO:
         return False             # few rows, small weights: the small-M product and the swiglu kernel
     lib = build.load("gemm_tc")
-    _, splits = tc_config(M, N, K, _sms(a.device), bn=256)
+    bn, splits = tc_config(M, N, K, _sms(a.device), swiglu=True)
     partial = _tc_partial(lib, M, N, splits, a.device)
-    code = lib.hk_gemm_tc(_ptr(a), _ptr(w_paired), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2, 256,
+    code = lib.hk_gemm_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), 2, bn,
                           splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "gemm+swiglu (tcgen05)")
     return True
-
-
-PAIR = 128
-
-
-def pair_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    """[F, d] gate and up -> [2F, d] with rows [128 gate | 128 up | 128 gate | ...]; F % 128 == 0."""
-    F, d = gate.shape
-    return torch.stack([gate.view(F // PAIR, PAIR, d), up.view(F // PAIR, PAIR, d)], dim=1).reshape(2 * F, d).contiguous()

@@ -21,7 +21,7 @@
 //     columns of 64 as the outermost dimension), so a box of {64, rows, columns} lands as columns x rows x 128
 //     bytes, which is the swizzled layout ldmatrix wants;
 //   * epilogues: store fp32, add onto fp32 `out` (the residual sum), or silu(gate) * up -> bf16 over a weight
-//     laid out [128 gate rows | 128 up rows] per 256 rows (a tile then holds BN/2 gate rows and their up rows).
+//     [all gate rows | all up rows] (a tile then holds BN/2 gate rows and, as its second half, their up rows).
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records it in `status`, its warps stop touching memory
 // but still meet at their barriers, and the kernel returns.
@@ -124,14 +124,11 @@ struct Control {
   int last;
 };
 
-// First row of the tile's first (second) half.  Plain layout: the halves are consecutive.  Paired layout: the
-// first half are gate rows, the second their up rows, 128 further down.
+// First row of the tile's first (second) half.  Plain product: the halves are consecutive.  SwiGLU: w is
+// [F gate rows | F up rows]; the first half are gate rows, the second their up rows, F further down.
 template <int BN, int EPI>
-__device__ __forceinline__ int tile_row(int tile, int half) {
-  if (EPI == EPI_SWIGLU) {
-    constexpr int PER_BLOCK = 256 / BN;      // tiles per [128 gate | 128 up] block
-    return (tile / PER_BLOCK) * 256 + (tile % PER_BLOCK) * (BN / 2) + half * 128;
-  }
+__device__ __forceinline__ int tile_row(int tile, int half, int F) {
+  if (EPI == EPI_SWIGLU) return tile * (BN / 2) + half * F;
   return tile * BN + half * (BN / 2);
 }
 
@@ -243,7 +240,7 @@ __device__ __forceinline__ void consume_units(const Sched& sc, uint32_t i_base, 
       };
       auto finish = [&](auto value) {
         if (EPI == EPI_SWIGLU) {
-          const int f0 = (tile_row<BN, EPI>(tile, 0) / 256) * 128 + tile_row<BN, EPI>(tile, 0) % 256;
+          const int f0 = tile * (BN / 2);
           for (int e = tid; e < (BN / 2) * COLS; e += CONSUMERS * 32) {
             const int m = e / (BN / 2), row = e % (BN / 2);
             if (m >= M) continue;
@@ -356,8 +353,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) break;
         mbar_expect_tx(&ctl->full[stage], S::STAGE_BYTES);
         const uint32_t base = ring + stage * S::STAGE_BYTES;
-        tma_load_3d(base, &map_w, &ctl->full[stage], 0, tile_row<BN, EPI>(tile, 0), c * KW);
-        tma_load_3d(base + S::W_HALF, &map_w, &ctl->full[stage], 0, tile_row<BN, EPI>(tile, 1), c * KW);
+        tma_load_3d(base, &map_w, &ctl->full[stage], 0, tile_row<BN, EPI>(tile, 0, N / 2), c * KW);
+        tma_load_3d(base + S::W_HALF, &map_w, &ctl->full[stage], 0, tile_row<BN, EPI>(tile, 1, N / 2), c * KW);
         tma_load_3d(base + S::W_BYTES, &map_a, &ctl->full[stage], 0, 0, c * KW);
         if ((int)i + 1 == ns) { tile = own_first; c = 0; }
         else if (++c == kc) { c = 0; ++tile; }
@@ -450,7 +447,7 @@ int launch_epi(int epilogue, const void* a, const void* w, void* out, int M, int
 }  // namespace
 
 // out = a w^T for M <= 32.  epilogue 0: out fp32 [M, N] stored; 1: out fp32 [M, N] +=; 2: out bf16 [M, N/2] =
-// silu(gate) * up with w's rows laid out [128 gate | 128 up] per 256 rows (N % 256 == 0).
+// silu(gate) * up with w = [N/2 gate rows | N/2 up rows] (N a multiple of the tile's rows, 16 * rw).
 // rw: 8, 4, 2 or 1 consumer warps across a tile's rows (tiles of 128, 64, 32 or 16 rows; the other warps split K).
 // workspace: at least hk_gemm_stream_workspace(M, rw) floats; counters: one int per tile of 16 rows of w, zero
 // before the first launch (left zero); status: device int that a timed-out wait sets to 1.
@@ -460,7 +457,7 @@ HK_API int hk_gemm_stream(const void* a, const void* w, void* out, int M, int N,
                           float* workspace, int* counters, int* status, int max_ctas, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 32 || K <= 0 || (K & 63) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue < 0 || epilogue > 2 || (epilogue == EPI_SWIGLU && (N & 255))) return HK_ERR_UNSUPPORTED;
+  if (epilogue < 0 || epilogue > 2 || (epilogue == EPI_SWIGLU && (rw < 1 || N % (16 * rw)))) return HK_ERR_UNSUPPORTED;
   if (workspace == nullptr || counters == nullptr || status == nullptr) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   const int mt = M <= 8 ? 1 : M <= 16 ? 2 : 4;

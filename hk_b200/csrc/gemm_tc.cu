@@ -7,8 +7,9 @@
 //               K-major from shared memory) and commits stage releases / accumulator-ready signals
 //   warps 2..5  epilogue: tcgen05.ld of the accumulator (one row per thread), then one of
 //               STORE (fp32), ADD (fp32 += : the residual sum), SWIGLU (bf16 silu(gate)*up from a
-//               weight whose rows are laid out [128 gate | 128 up] per tile)
-// Two accumulator buffers (2 x BN columns of tensor memory) let the epilogue of one tile overlap
+//               weight [all gate rows | all up rows]: a tile takes half its rows from each)
+// BN (the tile width, 16 to 256) and the ring depth are run-time values chosen by the caller per shape.
+// Two accumulator buffers (2 x 256 columns of tensor memory) let the epilogue of one tile overlap
 // the main loop of the next.  Every mbarrier wait is bounded: on time-out the CTA records an
 // error in `status`, all roles leave their loops, tensor memory is freed and the kernel returns.
 // No cluster multicast is used anywhere: every CTA loads its own tiles.
@@ -31,6 +32,12 @@ __host__ __device__ inline size_t slice_floats(int M, int N) { return (size_t)M 
 constexpr int BK = 64;       // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
+constexpr int MAX_BN = 256;             // the widest tile; also the distance of the two accumulator buffers in tensor memory
+constexpr int MAX_STAGES = 12;
+constexpr int A_BYTES = 128 * 64 * 2;  // the a tile of a stage
+constexpr int CONTROL_BYTES = 1024;
+constexpr int RING_BYTES = 227 * 1024 - 2 * 1024;   // what is left of an SM's shared memory after the control block and the alignment
+constexpr uint32_t TMEM_COLS = 2 * MAX_BN;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
@@ -111,42 +118,122 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+template <int W>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r) {
+  if (W == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int BN, int STAGES>
-struct SharedStorage {
-  alignas(1024) uint8_t a[STAGES][BM * BK * 2];
-  alignas(1024) uint8_t b[STAGES][BN * BK * 2];
-  alignas(8) uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+// Shared memory: [Control | ring of `stages` stages], a stage = the a tile (128 x 64 bf16 = 16 KB) followed by the
+// w tile (bn x 64 bf16, rounded up to 1 KB).  Tile width and ring depth are run-time values: the host picks the
+// width that fills whole waves of SMs and as many stages as fit.
+struct Control {
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(Control) <= CONTROL_BYTES, "control block too large");
 
-template <int BN, int STAGES, int EPI>
+__host__ __device__ inline uint32_t stage_bytes_of(int bn) { return (uint32_t)A_BYTES + (((uint32_t)bn * BK * 2 + 1023u) & ~1023u); }
+
+// W columns [c0, c0 + W) of this thread's accumulator row to fp32 out (stored or added).
+template <int W, bool ADD>
+__device__ __forceinline__ void store_chunk(uint32_t taddr, float* o, int c0, int n_out, bool row_ok, bool vec_ok) {
+  uint32_t v[W];
+  tmem_ld<W>(taddr + (uint32_t)c0, v);
+  tmem_ld_wait();
+  if (!row_ok) return;
+  if (c0 + W <= n_out && vec_ok) {
+#pragma unroll
+    for (int j = 0; j < W; j += 4) {
+      float4 x = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      float4* p = reinterpret_cast<float4*>(o + c0 + j);
+      if (ADD) {
+        float4 y = *p;
+        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+      }
+      *p = x;
+    }
+  } else {
+    for (int j = 0; j < W; ++j)
+      if (c0 + j < n_out) {
+        float x = __uint_as_float(v[j]);
+        o[c0 + j] = ADD ? o[c0 + j] + x : x;
+      }
+  }
+}
+
+// W gate columns at c0 and their up columns `h` further on -> W bf16 outputs silu(gate) * up.
+template <int W>
+__device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, int h, int n_out, bool row_ok, bool vec_ok) {
+  uint32_t g[W], u[W];
+  tmem_ld<W>(taddr + (uint32_t)c0, g);
+  tmem_ld<W>(taddr + (uint32_t)(h + c0), u);
+  tmem_ld_wait();
+  if (!row_ok) return;
+  if (c0 + W <= n_out && vec_ok) {
+#pragma unroll
+    for (int j = 0; j < W; j += 8) {
+      uint32_t packed[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
+        float h0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[j + 2 * e]);
+        float h1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
+        __nv_bfloat162 p = __floats2bfloat162_rn(h0, h1);
+        packed[e] = *reinterpret_cast<uint32_t*>(&p);
+      }
+      *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+  } else {
+    for (int j = 0; j < W; ++j)
+      if (c0 + j < n_out) {
+        float gv = __uint_as_float(g[j]);
+        o[c0 + j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * __uint_as_float(u[j]));
+      }
+  }
+}
+
+// `bn`: tile width, a multiple of 16 (32 with the SwiGLU epilogue) up to 256.  With the SwiGLU epilogue w is
+// [F gate rows | F up rows] (N = 2 F) and a tile holds bn / 2 gate rows and the bn / 2 up rows that match them,
+// brought by two copies; its accumulator columns are [gates | ups].
+template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-               int M, int N, int K, long long ldo, int splits, float* __restrict__ partial, int* __restrict__ status) {
+               int M, int N, int K, long long ldo, int bn, int stages, int splits, float* __restrict__ partial,
+               int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
-  using Storage = SharedStorage<BN, STAGES>;
-  Storage& sm = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Control& sm = *reinterpret_cast<Control*>(base);
+  uint8_t* ring = base + CONTROL_BYTES;
   volatile int* abort_flag = &sm.abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int h = bn >> 1, F = N >> 1;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = EPI == EPI_SWIGLU ? (F + h - 1) / h : (N + bn - 1) / bn;
   // With splits > 1 a work item is (output tile, slice of K); slice s of every tile comes before slice s + 1
   // of any, so the CTAs running together read different weights.  Each item stores its fp32 partial to
   // partial[s][M][N] (slices `slice_floats` apart); a second kernel adds the slices in order.
   const int mn_tiles = m_tiles * n_tiles;
   const int total_tiles = mn_tiles * splits;
   const int k_blocks_all = (K + BK - 1) / BK;
-  constexpr uint32_t TMEM_COLS = 2 * BN;   // 256 or 512: a power of two >= 32
-  constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
+  const uint32_t stage_bytes = stage_bytes_of(bn);
+  const uint32_t tx_bytes = (uint32_t)(BM + bn) * BK * 2;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
@@ -174,14 +261,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mn = tile % mn_tiles, ks = tile / mn_tiles;
-        const int m0 = (mn % m_tiles) * BM, n0 = (mn / m_tiles) * BN;
+        const int m0 = (mn % m_tiles) * BM, nt = mn / m_tiles;
         const int kb0 = (int)((long long)k_blocks_all * ks / splits), kb1 = (int)((long long)k_blocks_all * (ks + 1) / splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sm.empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&sm.full[stage], STAGE_BYTES);
-          tma_load_2d(sm.a[stage], &map_a, &sm.full[stage], kb * BK, m0);
-          tma_load_2d(sm.b[stage], &map_w, &sm.full[stage], kb * BK, n0);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          uint8_t* st = ring + (size_t)stage * stage_bytes;
+          mbar_expect_tx(&sm.full[stage], tx_bytes);
+          tma_load_2d(st, &map_a, &sm.full[stage], kb * BK, m0);
+          if (EPI == EPI_SWIGLU) {
+            tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, nt * h);
+            tma_load_2d(st + A_BYTES + h * (BK * 2), &map_w, &sm.full[stage], kb * BK, F + nt * h);
+          } else {
+            tma_load_2d(st + A_BYTES, &map_w, &sm.full[stage], kb * BK, nt * bn);
+          }
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -189,7 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N and M encoded
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -199,21 +292,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t use = (uint32_t)(local >> 1);
         if (!mbar_wait(&sm.tmem_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * MAX_BN);
         const int ks = tile / mn_tiles;
         const int kb0 = (int)((long long)k_blocks_all * ks / splits), kb1 = (int)((long long)k_blocks_all * (ks + 1) / splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sm.full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da = make_smem_desc(smem_u32(sm.a[stage]));
-          const uint64_t db = make_smem_desc(smem_u32(sm.b[stage]));
+          const uint32_t st = smem_u32(ring + (size_t)stage * stage_bytes);
+          const uint64_t da = make_smem_desc(st);
+          const uint64_t db = make_smem_desc(st + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance both start addresses by 32 bytes (16 bf16) inside the swizzled row
             umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&sm.empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(&sm.tmem_full[buf]);
       }
@@ -227,96 +321,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int buf = local & 1;
       const uint32_t use = (uint32_t)(local >> 1);
       const int mn = tile % mn_tiles, ks = tile / mn_tiles;
-      const int m0 = (mn % m_tiles) * BM, n0 = (mn / m_tiles) * BN;
+      const int m0 = (mn % m_tiles) * BM, nt = mn / m_tiles;
       if (!mbar_wait(&sm.tmem_full[buf], use & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      const bool row_ok = row < M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * MAX_BN);
       if (splits > 1) {
-        // a slice's partial sum, fp32 [M, N]
+        // a slice's partial sum, fp32 [M, N], a tile's columns as the accumulator has them
+        const int n0 = nt * bn;
         float* o = partial + (size_t)ks * slice_floats(M, N) + (size_t)row * N + n0;
         const int n_out = N - n0;
+        const bool vec_ok = (N & 3) == 0;
+        int c0 = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + (uint32_t)c0, v);
-          tmem_ld_wait();
-          if (row < M) {
-            if (c0 + 32 <= n_out && (N & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(o + c0 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                                     __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < n_out) o[c0 + j] = __uint_as_float(v[j]);
-            }
-          }
-        }
+        for (; c0 + 32 <= bn; c0 += 32) store_chunk<32, false>(taddr, o, c0, n_out, row_ok, vec_ok);
+        if (c0 < bn) store_chunk<16, false>(taddr, o, c0, n_out, row_ok, vec_ok);
       } else if (EPI == EPI_SWIGLU) {
-        // columns [0, BN/2) are gates, [BN/2, BN) the matching ups; output columns (n0 / 2) + c
-        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + (n0 >> 1);
-        const int n_out = (N >> 1) - (n0 >> 1);
+        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * ldo + nt * h;
+        const int n_out = F - nt * h;
+        const bool vec_ok = (ldo & 7) == 0 && ((nt * h) & 7) == 0;
+        int c0 = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(taddr + (uint32_t)c0, g);
-          tmem_ld32(taddr + (uint32_t)(BN / 2 + c0), u);
-          tmem_ld_wait();
-          if (row < M) {
-            if (c0 + 32 <= n_out && (ldo & 7) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
-                  float h0 = g0 / (1.0f + __expf(-g0)) * __uint_as_float(u[j + 2 * e]);
-                  float h1 = g1 / (1.0f + __expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
-                  __nv_bfloat162 p = __floats2bfloat162_rn(h0, h1);
-                  packed[e] = *reinterpret_cast<uint32_t*>(&p);
-                }
-                *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < n_out) {
-                  float gv = __uint_as_float(g[j]);
-                  o[c0 + j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * __uint_as_float(u[j]));
-                }
-            }
-          }
-        }
+        for (; c0 + 32 <= h; c0 += 32) swiglu_chunk<32>(taddr, o, c0, h, n_out, row_ok, vec_ok);
+        if (c0 < h) swiglu_chunk<16>(taddr, o, c0, h, n_out, row_ok, vec_ok);
       } else {
+        const int n0 = nt * bn;
         float* o = reinterpret_cast<float*>(out) + (size_t)row * ldo + n0;
         const int n_out = N - n0;
+        const bool vec_ok = (ldo & 3) == 0;
+        int c0 = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + (uint32_t)c0, v);
-          tmem_ld_wait();
-          if (row < M) {
-            if (c0 + 32 <= n_out && (ldo & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 x = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                                       __uint_as_float(v[j + 3]));
-                float4* p = reinterpret_cast<float4*>(o + c0 + j);
-                if (EPI == EPI_ADD) {
-                  float4 y = *p;
-                  x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-                }
-                *p = x;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < n_out) {
-                  float x = __uint_as_float(v[j]);
-                  o[c0 + j] = EPI == EPI_ADD ? o[c0 + j] + x : x;
-                }
-            }
-          }
-        }
+        for (; c0 + 32 <= bn; c0 += 32) store_chunk<32, EPI == EPI_ADD>(taddr, o, c0, n_out, row_ok, vec_ok);
+        if (c0 < bn) store_chunk<16, EPI == EPI_ADD>(taddr, o, c0, n_out, row_ok, vec_ok);
       }
       tc_fence_before();
       __syncwarp();
@@ -375,10 +412,10 @@ int sm_count() {
 }
 
 // Adds the K slices of a split product in slice order.  mode 0: out fp32 = sum; 1: out fp32 += sum;
-// 2: out bf16 [M, N/2] = silu(gate) * up over the paired layout (blocks of 128 gates then their 128 ups).
+// 2: out bf16 [M, N/2] = silu(gate) * up, the partial sums' columns in tiles of [bn / 2 gates | their bn / 2 ups].
 template <int MODE>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int M, int N, long long ldo,
-                                     int splits) {
+                                     int splits, int bn) {
   const long long total = MODE == 2 ? (long long)M * (N / 2) : (long long)M * N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -386,11 +423,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
   if (MODE == 2) {
     const int F = N / 2;
     const int m = (int)(i / F), j = (int)(i % F);
-    const size_t gi = (size_t)m * N + (size_t)(j / 128) * 256 + (j % 128);
+    const int h = bn >> 1;
+    const size_t gi = (size_t)m * N + (size_t)(j / h) * bn + (j % h);
     float gsum = 0.f, usum = 0.f;
     for (int s = 0; s < splits; ++s) {
       gsum += partial[s * slice + gi];
-      usum += partial[s * slice + gi + 128];
+      usum += partial[s * slice + gi + h];
     }
     reinterpret_cast<bf16*>(out)[(size_t)m * ldo + j] = __float2bfloat16_rn(gsum / (1.0f + __expf(-gsum)) * usum);
   } else {
@@ -426,15 +464,19 @@ __global__ void splitk_reduce_vec_kernel(const float* __restrict__ partial, floa
   *o = sum;
 }
 
-template <int BN, int STAGES, int EPI>
-int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int splits, float* partial,
-           int* status, cudaStream_t s) {
+template <int EPI>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int bn, int splits,
+           float* partial, int* status, cudaStream_t s) {
   static HkSmemCache allowed = {};
-  const size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
-  if (int e = hk_allow_smem(gemm_tc_kernel<BN, STAGES, EPI>, smem, allowed)) return e;
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
+  const uint32_t stage_bytes = stage_bytes_of(bn);
+  int stages = RING_BYTES / (int)stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  const size_t smem = (size_t)stages * stage_bytes + CONTROL_BYTES + 1024;
+  if (int e = hk_allow_smem(gemm_tc_kernel<EPI>, smem, allowed)) return e;
+  const int n_tiles = EPI == EPI_SWIGLU ? (N / 2 + bn / 2 - 1) / (bn / 2) : (N + bn - 1) / bn;
+  const int tiles = ((M + BM - 1) / BM) * n_tiles * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_tc_kernel<BN, STAGES, EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, splits, partial, status);
+  gemm_tc_kernel<EPI><<<grid, NUM_THREADS, smem, s>>>(ma, mw, out, M, N, K, ldo, bn, stages, splits, partial, status);
   int code = hk_launch_status();
   if (code != 0 || splits <= 1) return code;
   if (EPI != EPI_SWIGLU && (N & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0) {
@@ -445,37 +487,35 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
   }
   const long long total = EPI == EPI_SWIGLU ? (long long)M * (N / 2) : (long long)M * N;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  splitk_reduce_kernel<EPI><<<blocks, 256, 0, s>>>(partial, out, M, N, ldo, splits);
+  splitk_reduce_kernel<EPI><<<blocks, 256, 0, s>>>(partial, out, M, N, ldo, splits, bn);
   return hk_launch_status();
 }
 
 }  // namespace
 
 // out = a w^T.  epilogue 0: out fp32 [M, N] stored; 1: out fp32 [M, N] += ; 2: out bf16 [M, N/2] =
-// silu(gate) * up with w's rows laid out [128 gate | 128 up] per 256-row tile.  `status` is a device int
+// silu(gate) * up with w = [N/2 gate rows | N/2 up rows].  `bn` is the tile width: a multiple of 16 from 16 to 256
+// (of 32 for epilogue 2, where a tile holds bn/2 gate rows and their up rows).  `status` is a device int
 // that a timed-out wait sets to 1 (the caller reads it when it next synchronises).
-// Requirements (else HK_ERR_UNSUPPORTED): K % 8 == 0, a and w 16-byte aligned, for epilogue 2 N % 256 == 0.
+// Requirements (else HK_ERR_UNSUPPORTED): K % 8 == 0, a and w 16-byte aligned, for epilogue 2 N even.
 // splits > 1 cuts K into that many slices computed by different CTAs (for few output tiles: decode batches);
-// `partial` must then hold hk_gemm_tc_partial_floats(M, N, splits) floats of scratch.
+// `partial` must then hold hk_gemm_tc_partial_floats(M, N, splits) floats of scratch; with epilogue 2 the tiles must
+// then fit N exactly ((N / 2) % (bn / 2) == 0).
 HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
                       int splits, float* partial, int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue == EPI_SWIGLU && ((N & 255) || bn != 256)) return HK_ERR_UNSUPPORTED;
-  if (bn != 128 && bn != 256) return HK_ERR_UNSUPPORTED;
+  if (epilogue < EPI_STORE || epilogue > EPI_SWIGLU) return HK_ERR_UNSUPPORTED;
+  if (bn < 16 || bn > MAX_BN || (bn & 15)) return HK_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
   if (splits < 1 || splits > (K + BK - 1) / BK || (splits > 1 && partial == nullptr)) return HK_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU && splits > 1 && (N / 2) % (bn / 2) != 0) return HK_ERR_UNSUPPORTED;
   CUtensorMap ma, mw;
-  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, N, K, bn)) return HK_ERR_UNSUPPORTED;
+  if (!make_map(&ma, a, M, K, BM) || !make_map(&mw, w, N, K, epilogue == EPI_SWIGLU ? bn / 2 : bn)) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  if (bn == 256) {
-    if (epilogue == EPI_STORE) return launch<256, 4, EPI_STORE>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
-    if (epilogue == EPI_ADD) return launch<256, 4, EPI_ADD>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
-    if (epilogue == EPI_SWIGLU) return launch<256, 4, EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
-  } else {
-    if (epilogue == EPI_STORE) return launch<128, 6, EPI_STORE>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
-    if (epilogue == EPI_ADD) return launch<128, 6, EPI_ADD>(ma, mw, out, M, N, K, ldo, splits, partial, status, s);
-  }
-  return HK_ERR_UNSUPPORTED;
+  if (epilogue == EPI_STORE) return launch<EPI_STORE>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
+  if (epilogue == EPI_ADD) return launch<EPI_ADD>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
+  return launch<EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
 }
 
 // Floats of scratch that `hk_gemm_tc` needs for `splits` K slices.

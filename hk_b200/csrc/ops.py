@@ -169,28 +169,28 @@ def _as_weights(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return a.to(w.dtype)
 
 
-def gemm_swiglu(a: torch.Tensor, w_paired: torch.Tensor, out: torch.Tensor, block: int) -> None:
-    """out[M, F] = silu(gate) * up of a @ w_paired^T, w_paired [2F, K] laid out [block gates | block ups |
-    ...] (block = 0: [F gates | F ups]).  Fused into the tensor-core product's epilogue when that takes the
-    shape, else a product to float32 followed by the swiglu kernel."""
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, F] = silu(gate) * up of a @ w_gate_up^T, w_gate_up [2F, K] = [F gate rows | F up rows].  Fused into
+    the tensor-core product's epilogue when that takes the shape (a tile of the product then holds gate rows and
+    the up rows that match them), else a product to float32 followed by the swiglu kernel."""
     _need(a, "a", dims=2)
-    _need(w_paired, "w", dims=2)
+    _need(w_gate_up, "w", dims=2)
     _need(out, "out", a.dtype, 2)
-    if w_paired.dtype != a.dtype:              # weights kept in 32-bit on the bfloat16 path: this product runs in 32-bit
-        wide = torch.empty(out.shape, dtype=w_paired.dtype, device=out.device)
-        gemm_swiglu(_as_weights(a, w_paired), w_paired, wide, block)
+    if w_gate_up.dtype != a.dtype:              # weights kept in 32-bit on the bfloat16 path: this product runs in 32-bit
+        wide = torch.empty(out.shape, dtype=w_gate_up.dtype, device=out.device)
+        gemm_swiglu(_as_weights(a, w_gate_up), w_gate_up, wide)
         out.copy_(wide)
         return
     M, F = out.shape
-    if a.shape[0] != M or w_paired.shape != (2 * F, a.shape[1]):
+    if a.shape[0] != M or w_gate_up.shape != (2 * F, a.shape[1]):
         raise KernelError("gemm_swiglu: shapes do not fit")
     if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc", "stream"):
         from . import gemm_fast
-        if block == gemm_fast.PAIR and gemm_fast.run_swiglu(a, w_paired, out, _forced["gemm"]):
+        if gemm_fast.run_swiglu(a, w_gate_up, out, _forced["gemm"]):
             return
     gu = torch.empty((M, 2 * F), dtype=torch.float32, device=a.device)
-    gemm(a, w_paired, gu)
-    swiglu(gu, out, block)
+    gemm(a, w_gate_up, gu)
+    swiglu(gu, out, 0)
 
 
 # ---- per-head norm + rotation + cache write ---------------------------------------------

@@ -18,7 +18,6 @@ class SwiGLUFeedForward(Part):
     def __init__(self, hidden: int, intermediate: int, prefix: str):
         self.hidden, self.F, self.prefix = hidden, intermediate, prefix
         self.w_gate_up = self.w_down = None
-        self.block = 0
 
     def own_param_specs(self) -> Dict[str, ParamSpec]:
         p = self.prefix
@@ -31,23 +30,17 @@ class SwiGLUFeedForward(Part):
     def own_bind(self, tensors, precision: Precision) -> None:
         p = self.prefix
         gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
-        # Serving layout: rows in blocks of 128 gates followed by their 128 ups, so that one output tile
-        # of the tensor-core product holds both halves and SwiGLU runs in its epilogue
-        # (cf. the interleaved gate/up of shaders/swiglu_pair.comp:2).  Otherwise [all gates | all ups].
-        from ..csrc import gemm_fast
+        # One matrix [all gate rows | all up rows]: one product gives both halves, and the tensor-core kernels take a
+        # tile's rows half from each so that SwiGLU runs in their epilogue (cf. the reference's fused gate/up product,
+        # shaders/swiglu_pair.comp:2).
         if gate.dtype != up.dtype:                  # one of them kept in 32-bit: both are
             gate, up = gate.float(), up.float()
-        if gate.dtype == torch.bfloat16 and self.F % gemm_fast.PAIR == 0:
-            self.block = gemm_fast.PAIR
-            self.w_gate_up = gemm_fast.pair_gate_up(gate, up)
-        else:
-            self.block = 0
-            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"]
 
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         h = torch.empty((xb.shape[0], self.F), dtype=xb.dtype, device=xb.device)
-        ops.gemm_swiglu(xb, self.w_gate_up, h, self.block)
+        ops.gemm_swiglu(xb, self.w_gate_up, h)
         ops.gemm(h, self.w_down, residual, accumulate=True)
 
 

@@ -91,7 +91,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page-tokens", type=int, default=16)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits per request and kv head (default: as the decode graphs choose); gemm_tc: K slices")
-    ap.add_argument("--bn", type=int, default=0, help="gemm_tc: pin the tile width (128 or 256)")
+    ap.add_argument("--bn", type=int, default=0, help="gemm_tc: pin the tile width (a multiple of 16, of 32 with --swiglu, up to 256)")
     ap.add_argument("--warm", action="store_true", help="do not flush L2 between the timed runs")
     ap.add_argument("--layers", type=int, default=2, help="decode: layers of the model")
     ap.add_argument("--hidden", type=int, default=4096)
@@ -121,7 +121,7 @@ def main(argv=None) -> int:
         w = (torch.randn(a.n, a.k, device=dev) / 8).to(torch.bfloat16)
         if a.swiglu:
             out = torch.empty(a.m, a.n // 2, dtype=torch.bfloat16, device=dev)
-            fn = lambda: ops.gemm_swiglu(x, w, out, gemm_fast.PAIR)
+            fn = lambda: ops.gemm_swiglu(x, w, out)
         else:
             out = torch.zeros(a.m, a.n, dtype=torch.float32, device=dev)
             fn = lambda: ops.gemm(x, w, out, accumulate=a.add)

@@ -452,7 +452,7 @@ def test_gemm_stream_swiglu_epilogue(rw, m, f, k):
     gemm_fast._stream_rw = rw
     try:
         with ops().force(gemm="stream"):
-            ops().gemm_swiglu(a.to(DEV), gemm_fast.pair_gate_up(gate, up).to(DEV), out, gemm_fast.PAIR)
+            ops().gemm_swiglu(a.to(DEV), torch.cat([gate, up]).to(DEV), out)
     finally:
         gemm_fast._stream_rw = 0
     gemm_fast.check_status(torch.device(DEV))
@@ -481,28 +481,59 @@ def test_fast_gemms_refuse_unaligned_shapes_and_the_generic_kernel_takes_them():
 
 
 @pytest.mark.parametrize("m,f,k", [(128, 128, 64), (300, 384, 200), (2048, 1536, 512), (7, 256, 128), (64, 128, 64), (65, 128, 64),
-                                   (40, 1024, 4096)])
-def test_gemm_swiglu_paired_layout(m, f, k):
+                                   (40, 1024, 4096), (64, 12288, 512), (33, 1000, 256), (200, 328, 64), (19, 77, 128), (500, 2056, 72)])
+def test_gemm_swiglu_in_the_epilogue(m, f, k):
+    # w = [F gate rows | F up rows]; widths that are no multiple of a tile, of 128 or of 8
     from hk_b200.csrc import gemm_fast
     g = torch.Generator().manual_seed(m + f + k)
     a = torch.randn(m, k, generator=g).to(torch.bfloat16)
     gate = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
     up = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
-    paired = gemm_fast.pair_gate_up(gate, up)
-    assert torch.equal(paired[:128], gate[:128]) and torch.equal(paired[128:256], up[:128])
+    w = torch.cat([gate, up]).to(DEV)
     out = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
-    ops().gemm_swiglu(a.to(DEV), paired.to(DEV), out, gemm_fast.PAIR)
+    ops().gemm_swiglu(a.to(DEV), w, out)
     gemm_fast.check_status(torch.device(DEV))
     want = ref_ops.swiglu(torch.cat([ref_ops.gemm(a, gate), ref_ops.gemm(a, up)], dim=1))
     close(out, want, torch.bfloat16, atol=2e-3)
-    # the unfused route over the same layout, and the plain [gates | ups] layout
-    with ops().force(gemm="generic"):
+    with ops().force(gemm="generic"):          # the unfused route
         out2 = torch.empty_like(out)
-        ops().gemm_swiglu(a.to(DEV), paired.to(DEV), out2, gemm_fast.PAIR)
-        out3 = torch.empty_like(out)
-        ops().gemm_swiglu(a.to(DEV), torch.cat([gate, up]).to(DEV), out3, 0)
+        ops().gemm_swiglu(a.to(DEV), w, out2)
     close(out2, want, torch.bfloat16, atol=2e-3)
-    close(out3, want, torch.bfloat16, atol=2e-3)
+
+
+@pytest.mark.parametrize("bn", [32, 64, 96, 160, 192, 224, 256])
+@pytest.mark.parametrize("m,f,k,splits", [(70, 672, 256, 1), (130, 1000, 72, 1), (64, 1344, 1024, 2), (9, 4032, 512, 3)])
+def test_gemm_swiglu_tcgen05_every_tile_width(bn, m, f, k, splits):
+    # the tile width is a run-time value: half a tile's rows are gates, half their ups; K slices where tiles fit F
+    from hk_b200.csrc import gemm_fast
+    if splits > 1 and f % (bn // 2):
+        pytest.skip("K slices need tiles that fit the width")
+    g = torch.Generator().manual_seed(bn + m + f + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    up = (torch.randn(f, k, generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    out = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
+    gemm_fast._tc_bn, gemm_fast._tc_splits = bn, splits
+    try:
+        with ops().force(gemm="tc"):
+            ops().gemm_swiglu(a.to(DEV), torch.cat([gate, up]).to(DEV), out)
+    finally:
+        gemm_fast._tc_bn = gemm_fast._tc_splits = 0
+    gemm_fast.check_status(torch.device(DEV))
+    want = ref_ops.swiglu(torch.cat([ref_ops.gemm(a, gate), ref_ops.gemm(a, up)], dim=1))
+    close(out, want, torch.bfloat16, atol=2e-3)
+
+
+@pytest.mark.parametrize("bn", [16, 48, 80, 112, 144, 176, 208, 240])
+@pytest.mark.parametrize("m,n,k,splits", [(64, 1000, 256, 1), (300, 777, 72, 1), (33, 4096, 2048, 4), (128, 250, 520, 2)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_tcgen05_every_tile_width(bn, m, n, k, splits, accumulate):
+    from hk_b200.csrc import gemm_fast
+    gemm_fast._tc_bn, gemm_fast._tc_splits = bn, splits
+    try:
+        gemm_case("tc", m, n, k, accumulate, seed=bn)
+    finally:
+        gemm_fast._tc_bn = gemm_fast._tc_splits = 0
 
 
 # ---- the flash attention kernel (bfloat16) -----------------------------------------------------

@@ -541,7 +541,6 @@ def test_toy_routed_feed_forward_and_another_position_encoding(dtype):
     w["l0.attn.q_norm.weight"], w["l0.attn.k_norm.weight"] = blk0.mixer.q_norm, blk0.mixer.k_norm
     ffns = [(f"l0.moe.expert{e}.", blk0.feed_forward.expert[e]) for e in range(cfg.experts)] + [("l1.mlp.", blk1.feed_forward)]
     for p, f in ffns:
-        assert f.block == 0                      # widths of 24 and 56: the plain [gates | ups] layout
         w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"] = f.w_gate_up[:f.F], f.w_gate_up[f.F:], f.w_down
     w = {k: v.double().cpu().numpy() for k, v in w.items()}
     rng = np.random.default_rng(1)
