@@ -133,6 +133,22 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
 __device__ __forceinline__ float ex2(float x) {      // 2^x, one instruction; 2^-inf = 0
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -706,61 +722,83 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
         const int t = t_begin + n;
         if (!__all_sync(0xffffffffu, mbar_wait(&sm.s_full[qt], (uint32_t)(n & 1), abort_flag))) { ok = false; break; }
         tc_fence_after();
-        uint32_t su[TK];
-#pragma unroll
-        for (int c0 = 0; c0 < TK; c0 += 32) tmem_ld32(lane_addr + SP_COL[qt] + (uint32_t)c0, su + c0);
-        tmem_ld_wait();
+        // The row's 128 scores in four chunks of 32: while one chunk's exponentials run, the next chunk is on its way
+        // from tensor memory, and a thread holds two chunks, not the row.  The reference maximum m is an integer and
+        // moves only when a chunk's maximum runs ahead of it by more than 8 (so a probability is at most 2^8); what was
+        // summed under the old reference (l, O, this tile's earlier chunks of P) is then multiplied by a power of two,
+        // which is exact.  The scores of this tile are complete, and so is every product issued before them, the last
+        // P V among them: O may be touched.
         const int j0 = t * TK;
         const bool whole = valid && j0 >= max(lo, it.kv_lo) && j0 + TK - 1 <= min(pos, it.kv_hi - 1);
-        if (!whole) {
+        uint32_t sc[2][32];
+        tmem_ld32(lane_addr + SP_COL[qt], sc[0]);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < TK; ++i) {
-            const int j = j0 + i;
-            const bool see = valid && j >= lo && j <= pos && j >= it.kv_lo && j < it.kv_hi;
-            if (!see) su[i] = 0xff800000u;             // -inf
+        for (int c = 0; c < TK / 32; ++c) {
+          uint32_t* su = sc[c & 1];
+          if (c + 1 < TK / 32) tmem_ld32(lane_addr + SP_COL[qt] + (uint32_t)(32 * (c + 1)), sc[(c + 1) & 1]);
+          if (!whole) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int j = j0 + 32 * c + i;
+              const bool see = valid && j >= lo && j <= pos && j >= it.kv_lo && j < it.kv_hi;
+              if (!see) su[i] = 0xff800000u;             // -inf
+            }
           }
-        }
-        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+          float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-        for (int i = 0; i < TK; i += 4) {
+          for (int i = 0; i < 32; i += 8) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(su[i + e]));
-        }
-        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
-        // Lazy rescaling, as in the one-tile kernel: the reference maximum moves only when the row's maximum has run
-        // ahead of it by more than 2^8.  The scores of this tile are complete, and so is every product issued before
-        // them, the last P V among them: O may be touched.
-        const bool move = mt > m + 8.0f;
-        const float mn = move ? mt : m;
-        const float msafe = mn == -CUDART_INF_F ? 0.f : mn;
-        const float corr = move ? exp2f(m - msafe) : 1.0f;
-        l0 *= corr;
-        l1 *= corr;
-        if (__any_sync(0xffffffffu, n > 0 && move)) {
-#pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
+            for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], fmaxf(__uint_as_float(su[i + 2 * e]), __uint_as_float(su[i + 2 * e + 1])));
           }
-        }
-        m = mn;
+          const float cm = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+          const bool move = cm > m + 8.0f;
+          if (__any_sync(0xffffffffu, move)) {
+            const float mn = move ? ceilf(cm) : m;
+            const float corr = move ? exp2f(m - mn) : 1.0f;      // m = -inf: 0; nothing was summed yet
+            l0 *= corr;
+            l1 *= corr;
+            if (n > 0) {
+#pragma unroll 1
+              for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
+                tmem_ld_wait();
 #pragma unroll
-        for (int c0 = 0; c0 < TK; c0 += 64) {
-          uint32_t pw[32];
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                tmem_st32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
+              }
+            }
+            if (c > 0) tmem_st_wait();       // this tile's earlier chunks of P are in tensor memory before they are read back
+#pragma unroll 1
+            for (int cp = 0; cp < c; ++cp) {
+              uint32_t pp[16];
+              tmem_ld16(lane_addr + SP_COL[qt] + (uint32_t)(16 * cp), pp);
+              tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float p0 = ex2(fmaf(__uint_as_float(su[c0 + 2 * e]), scale_log2, -msafe));
-            const float p1 = ex2(fmaf(__uint_as_float(su[c0 + 2 * e + 1]), scale_log2, -msafe));
+              for (int i = 0; i < 16; ++i) {
+                __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&pp[i]);
+                float2 f = __bfloat1622float2(v);
+                v = __floats2bfloat162_rn(f.x * corr, f.y * corr);
+                pp[i] = *reinterpret_cast<uint32_t*>(&v);
+              }
+              tmem_st16(lane_addr + SP_COL[qt] + (uint32_t)(16 * cp), pp);
+            }
+            m = mn;
+          }
+          const float msafe = m == -CUDART_INF_F ? 0.f : m;
+          uint32_t pw[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = ex2(fmaf(__uint_as_float(su[2 * e]), scale_log2, -msafe));
+            const float p1 = ex2(fmaf(__uint_as_float(su[2 * e + 1]), scale_log2, -msafe));
             l0 += p0;
             l1 += p1;
             __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
             pw[e] = *reinterpret_cast<uint32_t*>(&pk);
           }
-          tmem_st32(lane_addr + SP_COL[qt] + (uint32_t)(c0 / 2), pw);
+          tmem_st16(lane_addr + SP_COL[qt] + (uint32_t)(16 * c), pw);
+          if (c + 1 < TK / 32) tmem_ld_wait();
         }
         tmem_st_wait();
         tc_fence_before();
@@ -884,3 +922,4 @@ HK_API int hk_attention_prefill_tc2(const void* q, const void* k_pages, const vo
   if (hd == 128) return launch2<128>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
   return launch2<64>(mk, mv, q, block_table, table_stride, items, n_items, out, H, G, page_tokens, window, scale_log2, pages_cap, status, s);
 }
+
