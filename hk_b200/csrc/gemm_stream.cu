@@ -41,7 +41,12 @@ namespace {
 constexpr int CONSUMERS = 8;
 constexpr int NUM_THREADS = (CONSUMERS + 1) * 32;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
-constexpr int SMEM_BUDGET = 200 * 1024;
+// Shared memory a CTA may take.  Not all of the SM's: with 200 KB nothing else fits beside a CTA of this kernel, so the
+// kernels after it (norm, small-M product: launched as dependents) could not become resident and set up until it had left.
+// Measured over whole decode steps of the 8B layer sizes at batch 8 (ms a step) against the budget in KB:
+// 112: 4.16, 120: 4.01, 128-152: 3.93-3.95, 168-184: 3.95-3.96, 200: 4.03; batch 12 and 16 gain 0.6-0.9 % at 152.
+constexpr int SMEM_BUDGET = 152 * 1024;
+constexpr int SMEM_BUDGET_WIDE = 200 * 1024;     // 17 to 32 rows: a stage is 48 KB, and three must fit
 
 enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 
@@ -110,7 +115,8 @@ struct Shape {
   static constexpr int COLS = 8 * MT;
   static constexpr int TILE_FLOATS = KW * BN * (COLS + 1);
   static constexpr int FIXED = TILE_FLOATS * 4 + 1024;   // tile buffer, barriers, flags
-  static constexpr int STAGES_RAW = (SMEM_BUDGET - FIXED) / STAGE_BYTES;
+  static constexpr int BUDGET = MT <= 2 ? SMEM_BUDGET : SMEM_BUDGET_WIDE;
+  static constexpr int STAGES_RAW = (BUDGET - FIXED) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int SMEM = STAGES * STAGE_BYTES + FIXED + 1024;     // + room to align the ring to 1024 bytes
   static_assert(W_COL % 1024 == 0 && A_COL % 1024 == 0, "columns must keep the swizzle atoms aligned");
