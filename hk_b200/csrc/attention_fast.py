@@ -68,9 +68,10 @@ class PlanInfo:
 def decode_splits(n_rows: int, n_kv_heads: int, sm_count: int) -> int:
     """Key splits per request for a decode batch whose plan must keep its shape from step to step: as many
     CTAs as are resident at once (two per SM), rounded down so that no second, thin wave follows; at most 8
-    (the reference allows 16, src/cuda/engine.zig:96-101; measured here at batch 1, 2 and 4 over contexts of 512 to
-    8,192: 8 is as fast as 16 at batch 1 and up to 30 % faster at batch 2 and 4, since the merge of the partials
-    costs more than the finer split saves)."""
+    (the reference allows 16, src/cuda/engine.zig:96-101; measured here at batch 1 to 4 over contexts of 512 to
+    8,192, attention and merge together: 8 is the fastest or within a microsecond of it everywhere but at batch 1
+    over 8,192 tokens (29.7 us against 26.5 with 16), and 16 costs 8 to 10 us more at batch 3 and 4, since the merge
+    of the partials costs more than the finer split saves)."""
     return max(1, min(8, 2 * sm_count // max(1, n_rows * n_kv_heads)))
 
 

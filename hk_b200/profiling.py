@@ -141,7 +141,7 @@ def main(argv=None) -> int:
             q = torch.randn(n, H * hd, device=dev).to(torch.bfloat16)
             pos = torch.full((n,), a.ctx - 1, dtype=torch.int32, device=dev)
             slot = torch.arange(n, dtype=torch.int32, device=dev)
-            splits = a.splits or max(1, min(16, 2 * sms // (n * G)))
+            splits = a.splits or attention_fast.decode_splits(n, G, sms)
             plan = attention_fast.build_plan(list(range(n)), list(range(n)), [1] * n, [a.ctx - 1] * n, n, 0, H, G, sms, upload,
                                              fixed_splits=splits)
             nbytes = 2.0 * 2 * n * a.ctx * G * hd
