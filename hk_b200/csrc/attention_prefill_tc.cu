@@ -511,10 +511,12 @@ int launch(const void* q, const void* kp, const void* vp, const int* bt, int str
 // order they were issued, so they overwrite P only once that product has read it, and a commit after them says
 // that everything before is complete (which is why the softmax may touch O once it has seen the next scores).
 //
-//   warps 0-3 / 4-7   softmax of tile A / B: the row's 128 scores -> registers, mask, maximum, lazy rescaling of O,
-//                     exponentials, P -> tensor memory; at the end O / sum -> out
+//   warps 0-3 / 4-7   softmax of tile A / B: the row's 128 scores in four chunks of 32 (two live at a time: holding the
+//                     row spilled registers, and that local-memory traffic slowed every phase): mask, chunk maximum,
+//                     lazy rescaling against an integer reference maximum, exponentials, P -> tensor memory; at the
+//                     end O / sum -> out
 //   warp 8 (1 lane)   issues S_A S_B | PV_A S_A' | PV_B S_B' | ...
-//   warp 9 (1 lane)   TMA: K and V tiles of 128 keys, page by page (a box of {64 columns, the page's keys, 1 half
+//   warp 9            TMA: K and V tiles of 128 keys, page by page, one lane per box (a box of {64 columns, the page's keys, 1 half
 //                     of the head}), into two K and two V stages laid out [half][key][128 bytes], 128-byte swizzle
 //
 // Q is loaded by the softmax threads (each its own row, cp.async).  The cache pages must be TMA-able as whole

@@ -4,8 +4,9 @@
     weights (gate/up, down, the output head), the weight-streaming mma.sync kernel (`gemm_smallm.cu`) for the
     smaller ones (q/k/v, o);
   * 9 to 16 rows: the streaming kernel at every shape;
-  * more rows (larger decode batches, prefill, mixed batches): the persistent tcgen05 kernel (`gemm_tc.cu`),
-    cutting K into slices when the output has fewer tiles than the GPU has SMs.
+  * more rows (larger decode batches, prefill, mixed batches): the persistent tcgen05 kernel (`gemm_tc.cu`) with
+    the tile width that fills whole waves of SMs (`tc_config`), cutting K into slices when the output has fewer
+    tiles than the GPU has SMs.
 The choice depends on the shape alone, so a token's logits do not depend on what else a process ran before.
 Shapes all of them refuse (K not a multiple of 8, unaligned operands) go to the generic kernel.
 """
