@@ -576,11 +576,12 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
   const int page_lo = it.kv_lo / page_tokens;
   const int n_pages = it.kv_hi > it.kv_lo ? min((it.kv_hi - 1) / page_tokens - page_lo + 1, pages_cap) : 0;
   for (int i = threadIdx.x; i < n_pages; i += NT2) pages[i] = bt[page_lo + i];
-  // K and V stages start as zeros: a box that is not copied (a page outside the key range that the request does
-  // not hold) leaves its rows as they are, and whatever is there is multiplied by a probability of zero
+  // The V stages start as zeros: a box that is not copied (a page outside the key range, or one that the request
+  // does not hold) leaves its rows as they are, and whatever is there is multiplied by a probability of zero, which
+  // must not meet a NaN pattern.  K needs none: a score of such a key is masked before it is looked at.
   {
-    uint4* z = reinterpret_cast<uint4*>(sm.k[0]);
-    constexpr int N16 = 4 * TK * HD * 2 / 16;      // k[2] and v[2] are contiguous
+    uint4* z = reinterpret_cast<uint4*>(sm.v[0]);
+    constexpr int N16 = 2 * TK * HD * 2 / 16;
     for (int i = threadIdx.x; i < N16; i += NT2) z[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   if (threadIdx.x == 0) {
@@ -811,22 +812,21 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
         const float l = l0 + l1;
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         bf16* op = out + ((size_t)(it.q_row0 + (valid ? tq : 0)) * H + g * group + (valid ? row % group : 0)) * HD;
+        // the whole row of O at once (the registers that held scores are free now): one wait instead of HD / 32
+        uint32_t o[HD];
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld32(lane_addr + O_COL[qt] + (uint32_t)c0, o);
-          tmem_ld_wait();
-          if (valid) {
+        for (int c0 = 0; c0 < HD; c0 += 32) tmem_ld32(lane_addr + O_COL[qt] + (uint32_t)c0, o + c0);
+        tmem_ld_wait();
+        if (valid) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint32_t w[4];
+          for (int i = 0; i < HD; i += 8) {
+            uint32_t w[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
-                w[e] = *reinterpret_cast<uint32_t*>(&pk);
-              }
-              *reinterpret_cast<uint4*>(op + c0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&pk);
             }
+            *reinterpret_cast<uint4*>(op + i) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
