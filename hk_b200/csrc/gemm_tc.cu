@@ -174,6 +174,24 @@ __device__ __forceinline__ void store_chunk(uint32_t taddr, float* o, int c0, in
   }
 }
 
+// The same for 32 columns added onto values of `out` that are in registers already (asked for two chunks ahead).
+__device__ __forceinline__ void add_chunk_prefetched(uint32_t taddr, float* o, int c0, const float4* y) {
+  uint32_t v[32];
+  tmem_ld32(taddr + (uint32_t)c0, v);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    float4 x = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+    const float4 r = y[j >> 2];
+    x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w;
+    *reinterpret_cast<float4*>(o + c0 + j) = x;
+  }
+}
+__device__ __forceinline__ void load_chunk(const float* o, int c0, float4* y) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) y[j] = *reinterpret_cast<const float4*>(o + c0 + 4 * j);
+}
+
 // W gate columns at c0 and their up columns `h` further on -> W bf16 outputs silu(gate) * up.
 template <int W>
 __device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, int h, int n_out, bool row_ok, bool vec_ok) {
@@ -324,10 +342,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t use = (uint32_t)(local >> 1);
       const int mn = tile % mn_tiles, ks = tile / mn_tiles;
       const int m0 = (mn % m_tiles) * BM, nt = mn / m_tiles;
-      if (!mbar_wait(&sm.tmem_full[buf], use & 1u, abort_flag)) { ok = false; break; }
-      tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < M;
+      // Adding onto `out` (the residual sum): the values to add onto do not depend on the product, so the first two
+      // chunks of this thread's row are asked for before the accumulator is waited for, and then two chunks ahead:
+      // after a CTA's last tile nothing hides the epilogue, and a load per chunk in turn made it 10 us long.
+      // (for a whole warp or not at all: the tensor-memory loads below are warp-wide instructions)
+      const bool pre = EPI == EPI_ADD && splits == 1 && (ldo & 3) == 0 && nt * bn + bn <= N && bn >= 64 &&
+                       __all_sync(0xffffffffu, row_ok);
+      float4 y0[8], y1[8];
+      float* o_add = reinterpret_cast<float*>(out) + (size_t)row * ldo + nt * bn;
+      if (pre) {
+        load_chunk(o_add, 0, y0);
+        load_chunk(o_add, 32, y1);
+      }
+      if (!mbar_wait(&sm.tmem_full[buf], use & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * MAX_BN);
       if (splits > 1) {
         // a slice's partial sum, fp32 [M, N], a tile's columns as the accumulator has them
@@ -353,6 +383,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int n_out = N - n0;
         const bool vec_ok = (ldo & 3) == 0;
         int c0 = 0;
+        if (pre) {
+#pragma unroll 1
+          for (; c0 + 64 <= bn; c0 += 64) {
+            add_chunk_prefetched(taddr, o, c0, y0);
+            if (c0 + 96 <= bn) load_chunk(o, c0 + 64, y0);
+            add_chunk_prefetched(taddr, o, c0 + 32, y1);
+            if (c0 + 128 <= bn) load_chunk(o, c0 + 96, y1);
+          }
+          if (c0 + 32 <= bn) {
+            add_chunk_prefetched(taddr, o, c0, y0);
+            c0 += 32;
+          }
+        }
 #pragma unroll 1
         for (; c0 + 32 <= bn; c0 += 32) store_chunk<32, EPI == EPI_ADD>(taddr, o, c0, n_out, row_ok, vec_ok);
         if (c0 < bn) store_chunk<16, EPI == EPI_ADD>(taddr, o, c0, n_out, row_ok, vec_ok);
